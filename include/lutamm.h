@@ -1,0 +1,191 @@
+/*
+ * lutamm.h - C ABI of the B200-native LUT-NN approximate matrix multiply (AMM).
+ *
+ * One AMM replaces one linear layer  out[M][N] = f(x[M][K]):
+ *   1. closest-centroid search: for every token m and codebook cb, the index of the
+ *      centroid nearest (squared L2, fp32, hysteresis scan) to the length-v slice
+ *      x[m][cb*v : cb*v+v];
+ *   2. gather-accumulate: acc[m][n] = sum_cb LUT[cb][idx[m][cb]][n]  (int8 -> int32);
+ *   3. dequantise: out = (float)acc*scale + lut_bias*(float)CB + bias[n].
+ *
+ * Every entry point below names the piece of the reference inference engine it stands
+ * in for (paths inside the reference project).  All calls return 0 on success or a
+ * negative LUTAMM_E* code; lutamm_last_error() gives the text.  Nothing here aborts
+ * the process.  Data pointers may be host or device addresses unless stated; host
+ * buffers are staged through pinned memory owned by the context.
+ *
+ * Layouts (all dense, row-major, the "canonical" forms the reference's weight
+ * converter writes): input [M][K] fp32, centroid [CB][CT][v] fp32, LUT [CB][CT][N]
+ * int8, bias [N] fp32, output [M][N] fp32, indices [M][CB] uint8.
+ */
+#ifndef LUTAMM_H
+#define LUTAMM_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LUTAMM_OK            0
+#define LUTAMM_EINVAL       -1   /* bad argument, shape or alignment                       */
+#define LUTAMM_ECUDA        -2   /* a CUDA runtime / driver call failed                    */
+#define LUTAMM_ENOLAYER     -3   /* layer_id has no weights loaded                         */
+#define LUTAMM_EUNSUPPORTED -4   /* shape outside what the requested kernel variant covers */
+#define LUTAMM_EDEVICE      -5   /* a kernel reported a bounded wait that ran out          */
+#define LUTAMM_ENOMEM       -6
+
+/* flags for lutamm_amm / lutamm_pim_lut */
+#define LUTAMM_FLAG_ASYNC         1u  /* do not synchronise the stream before returning (device buffers only) */
+#define LUTAMM_FLAG_OUTPUT_TILED  2u  /* write the output in the reference's DPU-tiled layout
+                                         [dpu][f_mtile][n_in_stile][f_in_mtile] (pim_lut_kernel.c:183,
+                                         test_amm.cpp:193-202) instead of row-major [M][N]          */
+
+/* kernel variants for step 2 */
+#define LUTAMM_VARIANT_AUTO    0
+#define LUTAMM_VARIANT_GATHER  1   /* TMA-staged shared-memory gather, CUDA cores          */
+#define LUTAMM_VARIANT_UMMA    2   /* one-hot x LUT int8 contraction on tcgen05 / TMEM     */
+
+/* index formats for lutamm_index_calculation */
+#define LUTAMM_INDEX_U8_ROWMAJOR  0  /* uint8  idx[M][CB]                                   */
+#define LUTAMM_INDEX_U16_TILED    1  /* uint16, the reference's [n_tile][cb_tile][n_in][cb_in]
+                                        layout (index_calc_host.cpp:41-49)                  */
+
+typedef struct lutamm_ctx lutamm_ctx;
+
+/* Field-for-field the reference's IndexCalcParams (src/host/defines.h:12-24). */
+typedef struct lutamm_index_params {
+    uint32_t n;
+    uint32_t input_feature_len;
+    uint32_t sub_vec_len;
+    uint32_t num_codebook;
+    uint32_t num_centroid;
+    uint32_t num_threads;     /* host threads in the reference; ignored here            */
+    uint32_t n_stile_size;    /* only used by the tiled index / output compat layouts   */
+    uint32_t cb_mtile_size;
+} lutamm_index_params;
+
+/* Field-for-field the reference's LUTParams (src/host/defines.h:26-50). */
+typedef struct lutamm_lut_params {
+    uint32_t n;
+    uint32_t output_feature_len;
+    uint32_t num_codebook;
+    uint32_t num_centroid;
+    float    scale;
+    float    bias;            /* the per-tensor LUT bias; added CB times (pim_lut_host.cpp:201) */
+    uint32_t num_threads;
+    uint32_t dpu_num;         /* UPMEM mapping fields: accepted, used only by the compat layouts */
+    uint32_t input_parallelism;
+    uint32_t lut_parallelism;
+    uint32_t feature_stile_size;
+    uint32_t n_stile_size;
+    uint32_t n_mtile_size;
+    uint32_t feature_mtile_size;
+    uint32_t cb_mtile_size;
+    uint32_t lut_load_type;   /* enum LUTLoadType {STATIC, FINE_GRAIN, COARSE_GRAIN} */
+    uint32_t feature_load_tile_size;
+    uint32_t cb_load_tile_size;
+} lutamm_lut_params;
+
+/* GPU execution plan for one layer: what the reference's auto-tuner output
+ * (kernel_params in the YAML, src/tuner/auto_tuner.cpp:46-82) becomes on a GPU. */
+typedef struct lutamm_plan {
+    uint32_t variant;         /* LUTAMM_VARIANT_*                                         */
+    uint32_t ccs_tokens;      /* tokens each search thread walks (0 = default)            */
+    uint32_t gather_cfg;      /* gather kernel tile configuration id (0 = default)        */
+    uint32_t umma_n_tile;     /* tcgen05 N tile: 64, 128 or 256 (0 = default)             */
+    uint32_t umma_split;      /* tcgen05 split of the codebook axis across CTAs (0 = auto) */
+    uint32_t umma_stages;     /* tcgen05 shared-memory pipeline depth (0 = default)       */
+    uint32_t reserved[2];
+} lutamm_plan;
+
+/* Device times of the last timed call, milliseconds (CUDA events on the context's stream).
+ * Mirrors the reference's amm_time accumulators (src/host/utils.h:14-20). */
+typedef struct lutamm_timings {
+    float index_calc_ms;      /* amm_profiles.index_calc_latency                          */
+    float lut_kernel_ms;      /* amm_profiles.kernel_latency                              */
+    float data_transfer_ms;   /* amm_profiles.data_transfer_latency (host<->device copies) */
+    float total_ms;
+} lutamm_timings;
+
+/* ---- context --------------------------------------------------------------------- */
+
+/* Replaces allocate_dpu()/allocate_rank() (src/host/dpu_common.h:11-33): binds a context
+ * to one CUDA device and creates its stream. */
+int lutamm_create(lutamm_ctx** out, int device);
+
+/* Replaces free_dpu_set() (src/host/dpu_common.h:35-38). Frees weights and scratch. */
+int lutamm_destroy(lutamm_ctx* ctx);
+
+/* Run on a caller-owned CUDA stream (a cudaStream_t passed as void*); NULL restores the
+ * context's own stream.  No counterpart in the reference (dpu_launch is synchronous,
+ * pim_lut_host.cpp:163). */
+int lutamm_set_stream(lutamm_ctx* ctx, void* cuda_stream);
+
+/* Block until everything queued on the context's stream has finished
+ * (dpu_sync, pim_lut_host.cpp:22,36,117,181). */
+int lutamm_sync(lutamm_ctx* ctx);
+
+const char* lutamm_last_error(const lutamm_ctx* ctx);
+
+/* Library identification; also the symbol CPU-only tests call to prove the library loads. */
+const char* lutamm_version(void);
+
+/* ---- weights --------------------------------------------------------------------- */
+
+/* Upload one linear layer's centroids, LUT and bias once and keep them resident.
+ * Replaces load_binary() before every AMM (src/host/dpu_common.h:40-54,
+ * transformer_layer.cpp:300,430,499,555) and the per-call LUT push prepare_lut_table()
+ * (src/host/pim_lut_host.cpp:26-37).  Validates what parse_amm_configs() asserts
+ * (src/host/parser.cpp:56-69) plus K == CB*v, CT <= 256, N % 16 == 0. */
+int lutamm_load_weights(lutamm_ctx* ctx, int layer_id,
+                        const float* centroid, const int8_t* lut, const float* bias,
+                        const lutamm_index_params* index_params,
+                        const lutamm_lut_params* lut_params);
+
+int lutamm_unload_weights(lutamm_ctx* ctx, int layer_id);
+
+/* ---- the operator ---------------------------------------------------------------- */
+
+/* Replaces amm_host() (src/host/amm_host.cpp:10-30; declared amm_host.h:8-10):
+ * search + gather + dequantise for n_tokens rows. */
+int lutamm_amm(lutamm_ctx* ctx, int layer_id, const float* input, float* output,
+               uint32_t n_tokens, uint32_t flags);
+
+/* lutamm_amm plus the two intermediate results, for parity checks: idx_out uint8
+ * [n_tokens][CB], acc_out int32 [n_tokens][N]; either may be NULL.  Stands in for the
+ * reference's amm_cpu()/check_dpu_result() verification hook (test_amm.cpp:126-213). */
+int lutamm_amm_debug(lutamm_ctx* ctx, int layer_id, const float* input, float* output,
+                     uint32_t n_tokens, uint8_t* idx_out, int32_t* acc_out, uint32_t flags);
+
+/* Replaces index_calculation() (src/host/index_calc_host.cpp:8-53). */
+int lutamm_index_calculation(lutamm_ctx* ctx, int layer_id, const float* input, void* index_out,
+                             uint32_t n_tokens, uint32_t index_format);
+
+/* Replaces pim_lut() (src/host/pim_lut_host.cpp:121-222) with prepare_input_index()
+ * (:40-118) folded into the kernel's address arithmetic: index is uint8 [n_tokens][CB]. */
+int lutamm_pim_lut(lutamm_ctx* ctx, int layer_id, const uint8_t* index, float* output,
+                   uint32_t n_tokens, uint32_t flags);
+
+/* ---- plans, tuning, timing ------------------------------------------------------- */
+
+int lutamm_set_plan(lutamm_ctx* ctx, int layer_id, const lutamm_plan* plan);
+int lutamm_get_plan(lutamm_ctx* ctx, int layer_id, lutamm_plan* plan);
+
+/* Replaces the auto-tuner's mapping search (src/tuner/auto_tuner.cpp:368-603): times the
+ * candidate kernel variants and tile configurations for n_tokens rows with CUDA events
+ * and installs the fastest.  best may be NULL. */
+int lutamm_tune(lutamm_ctx* ctx, int layer_id, uint32_t n_tokens, lutamm_plan* best);
+
+/* Turn per-stage CUDA-event timing on (non-zero) or off; the reference's AMM_BREAKDOWN
+ * compile-time switch (amm_host.cpp:14-26, pim_lut_host.cpp:124-212) as a runtime flag. */
+int lutamm_enable_timing(lutamm_ctx* ctx, int on);
+int lutamm_get_timings(lutamm_ctx* ctx, lutamm_timings* out);
+
+/* Kernels of this library launched on this context since creation. */
+uint64_t lutamm_launch_count(const lutamm_ctx* ctx);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LUTAMM_H */

@@ -1,0 +1,280 @@
+"""B200-native LUT-NN approximate matrix multiply (AMM): Python host side.
+
+This package is a thin mirror of the reference inference engine's operator interface
+(inference-engine/src/host/amm_host.h:8-10, index_calc_host.h:5, pim_lut_host.h:14-15)
+over the C ABI in include/lutamm.h.  All arithmetic happens in libpimdl_b200.so
+(hand-written CUDA for sm_100a); there is no CPU or PyTorch implementation of the
+operator here, and importing the compute entry points without the built library raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from dataclasses import dataclass, field
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libpimdl_b200.so")
+
+OK, EINVAL, ECUDA, ENOLAYER, EUNSUPPORTED, EDEVICE, ENOMEM = 0, -1, -2, -3, -4, -5, -6
+FLAG_ASYNC, FLAG_OUTPUT_TILED = 1, 2
+VARIANT_AUTO, VARIANT_GATHER, VARIANT_UMMA = 0, 1, 2
+INDEX_U8_ROWMAJOR, INDEX_U16_TILED = 0, 1
+
+# every symbol include/lutamm.h declares
+ABI_SYMBOLS = [
+    "lutamm_create", "lutamm_destroy", "lutamm_set_stream", "lutamm_sync", "lutamm_last_error",
+    "lutamm_version", "lutamm_load_weights", "lutamm_unload_weights", "lutamm_amm", "lutamm_amm_debug",
+    "lutamm_index_calculation", "lutamm_pim_lut", "lutamm_set_plan", "lutamm_get_plan", "lutamm_tune",
+    "lutamm_enable_timing", "lutamm_get_timings", "lutamm_launch_count",
+]
+
+
+class LutAmmError(RuntimeError):
+    def __init__(self, code: int, msg: str):
+        super().__init__(f"lutamm error {code}: {msg}")
+        self.code = code
+
+
+class IndexCalcParams(ctypes.Structure):
+    """Field-for-field the reference's IndexCalcParams (src/host/defines.h:12-24)."""
+    _fields_ = [(n, ctypes.c_uint32) for n in (
+        "n", "input_feature_len", "sub_vec_len", "num_codebook", "num_centroid", "num_threads",
+        "n_stile_size", "cb_mtile_size")]
+
+
+class LUTParams(ctypes.Structure):
+    """Field-for-field the reference's LUTParams (src/host/defines.h:26-50)."""
+    _fields_ = [("n", ctypes.c_uint32), ("output_feature_len", ctypes.c_uint32),
+                ("num_codebook", ctypes.c_uint32), ("num_centroid", ctypes.c_uint32),
+                ("scale", ctypes.c_float), ("bias", ctypes.c_float),
+                ("num_threads", ctypes.c_uint32), ("dpu_num", ctypes.c_uint32),
+                ("input_parallelism", ctypes.c_uint32), ("lut_parallelism", ctypes.c_uint32),
+                ("feature_stile_size", ctypes.c_uint32), ("n_stile_size", ctypes.c_uint32),
+                ("n_mtile_size", ctypes.c_uint32), ("feature_mtile_size", ctypes.c_uint32),
+                ("cb_mtile_size", ctypes.c_uint32), ("lut_load_type", ctypes.c_uint32),
+                ("feature_load_tile_size", ctypes.c_uint32), ("cb_load_tile_size", ctypes.c_uint32)]
+
+
+class Plan(ctypes.Structure):
+    _fields_ = [("variant", ctypes.c_uint32), ("ccs_tokens", ctypes.c_uint32), ("gather_cfg", ctypes.c_uint32),
+                ("umma_n_tile", ctypes.c_uint32), ("umma_split", ctypes.c_uint32), ("umma_stages", ctypes.c_uint32),
+                ("reserved", ctypes.c_uint32 * 2)]
+
+    def as_dict(self):
+        return {k: getattr(self, k) for k in ("variant", "ccs_tokens", "gather_cfg", "umma_n_tile", "umma_split",
+                                              "umma_stages")}
+
+
+class Timings(ctypes.Structure):
+    _fields_ = [("index_calc_ms", ctypes.c_float), ("lut_kernel_ms", ctypes.c_float),
+                ("data_transfer_ms", ctypes.c_float), ("total_ms", ctypes.c_float)]
+
+
+_lib = None
+
+
+def load_library() -> ctypes.CDLL:
+    """dlopen libpimdl_b200.so and type its entry points.  Raises if it has not been built:
+    there is no fallback implementation."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -c 'import __graft_entry__ as g; g.build()'` "
+            "(nvcc, sm_100a).  This package has no CPU fallback.")
+    L = ctypes.CDLL(LIB_PATH)
+    vp, u32, i32 = ctypes.c_void_p, ctypes.c_uint32, ctypes.c_int
+    L.lutamm_version.restype = ctypes.c_char_p
+    L.lutamm_version.argtypes = []
+    L.lutamm_create.argtypes = [ctypes.POINTER(vp), i32]
+    L.lutamm_destroy.argtypes = [vp]
+    L.lutamm_set_stream.argtypes = [vp, vp]
+    L.lutamm_sync.argtypes = [vp]
+    L.lutamm_last_error.argtypes = [vp]
+    L.lutamm_last_error.restype = ctypes.c_char_p
+    L.lutamm_load_weights.argtypes = [vp, i32, vp, vp, vp, ctypes.POINTER(IndexCalcParams), ctypes.POINTER(LUTParams)]
+    L.lutamm_unload_weights.argtypes = [vp, i32]
+    L.lutamm_amm.argtypes = [vp, i32, vp, vp, u32, u32]
+    L.lutamm_amm_debug.argtypes = [vp, i32, vp, vp, u32, vp, vp, u32]
+    L.lutamm_index_calculation.argtypes = [vp, i32, vp, vp, u32, u32]
+    L.lutamm_pim_lut.argtypes = [vp, i32, vp, vp, u32, u32]
+    L.lutamm_set_plan.argtypes = [vp, i32, ctypes.POINTER(Plan)]
+    L.lutamm_get_plan.argtypes = [vp, i32, ctypes.POINTER(Plan)]
+    L.lutamm_tune.argtypes = [vp, i32, u32, ctypes.POINTER(Plan)]
+    L.lutamm_enable_timing.argtypes = [vp, i32]
+    L.lutamm_get_timings.argtypes = [vp, ctypes.POINTER(Timings)]
+    L.lutamm_launch_count.argtypes = [vp]
+    L.lutamm_launch_count.restype = ctypes.c_uint64
+    for name in ABI_SYMBOLS:
+        if name not in ("lutamm_version", "lutamm_last_error", "lutamm_launch_count"):
+            getattr(L, name).restype = i32
+    _lib = L
+    return L
+
+
+def _ptr(a) -> int:
+    """Address of a numpy array (host) or of anything with data_ptr() (a torch tensor)."""
+    if a is None:
+        return 0
+    if isinstance(a, np.ndarray):
+        assert a.flags["C_CONTIGUOUS"], "arrays handed to the C ABI must be contiguous"
+        return a.ctypes.data
+    if hasattr(a, "data_ptr"):
+        assert a.is_contiguous(), "tensors handed to the C ABI must be contiguous"
+        return a.data_ptr()
+    return int(a)
+
+
+def make_params(M: int, K: int, N: int, CB: int, CT: int, scale: float, lut_bias: float = 0.0, *,
+                n_stile: int | None = None, f_stile: int | None = None, n_mtile: int | None = None,
+                f_mtile: int | None = None, cb_mtile: int | None = None, num_threads: int = 1):
+    """Parameter blocks as parse_amm_configs() would fill them (src/host/parser.cpp:22-46).
+    Tile sizes default to "one tile": the canonical row-major layouts."""
+    n_stile = n_stile or max(M, 1)
+    f_stile = f_stile or N
+    n_mtile = n_mtile or n_stile
+    f_mtile = f_mtile or f_stile
+    cb_mtile = cb_mtile or CB
+    ip = IndexCalcParams(M, K, K // CB, CB, CT, num_threads, n_stile, cb_mtile)
+    lp = LUTParams()
+    lp.n, lp.output_feature_len, lp.num_codebook, lp.num_centroid = M, N, CB, CT
+    lp.scale, lp.bias = scale, lut_bias
+    lp.num_threads = num_threads
+    lp.input_parallelism = max(M // n_stile, 1)
+    lp.lut_parallelism = max(N // f_stile, 1)
+    lp.dpu_num = lp.input_parallelism * lp.lut_parallelism
+    lp.feature_stile_size, lp.n_stile_size = f_stile, n_stile
+    lp.n_mtile_size, lp.feature_mtile_size, lp.cb_mtile_size = n_mtile, f_mtile, cb_mtile
+    lp.lut_load_type = 0
+    lp.feature_load_tile_size, lp.cb_load_tile_size = f_mtile, cb_mtile
+    return ip, lp
+
+
+@dataclass
+class _LayerInfo:
+    K: int
+    N: int
+    CB: int
+    CT: int
+    ip: IndexCalcParams = field(repr=False, default=None)
+    lp: LUTParams = field(repr=False, default=None)
+
+
+class LutAmmContext:
+    """One context per process per GPU: the stand-in for the reference's dpu_set_t
+    (allocate_dpu/free_dpu_set, src/host/dpu_common.h:11-38)."""
+
+    def __init__(self, device: int = 0):
+        self._L = load_library()
+        h = ctypes.c_void_p()
+        rc = self._L.lutamm_create(ctypes.byref(h), device)
+        if rc != OK:
+            raise LutAmmError(rc, self._L.lutamm_last_error(None).decode())
+        self._h = h
+        self.device = device
+        self.layers: dict[int, _LayerInfo] = {}
+
+    # -- plumbing
+    def _check(self, rc: int):
+        if rc != OK:
+            raise LutAmmError(rc, self._L.lutamm_last_error(self._h).decode())
+
+    def close(self):
+        if getattr(self, "_h", None):
+            self._L.lutamm_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    def set_stream(self, cuda_stream: int | None):
+        self._check(self._L.lutamm_set_stream(self._h, cuda_stream or None))
+
+    def sync(self):
+        self._check(self._L.lutamm_sync(self._h))
+
+    @property
+    def launch_count(self) -> int:
+        return int(self._L.lutamm_launch_count(self._h))
+
+    # -- weights
+    def load_weights(self, layer_id: int, centroid, lut, bias, scale: float, lut_bias: float = 0.0,
+                     ip: IndexCalcParams | None = None, lp: LUTParams | None = None):
+        """centroid [CB][CT][v] fp32, lut [CB][CT][N] int8, bias [N] fp32 (numpy or torch)."""
+        CB, CT, v = tuple(centroid.shape)
+        N = int(lut.shape[2])
+        K = CB * v
+        if ip is None or lp is None:
+            ip, lp = make_params(0, K, N, CB, CT, scale, lut_bias)
+        self._check(self._L.lutamm_load_weights(self._h, layer_id, _ptr(centroid), _ptr(lut), _ptr(bias),
+                                                ctypes.byref(ip), ctypes.byref(lp)))
+        self.layers[layer_id] = _LayerInfo(K, N, CB, CT, ip, lp)
+
+    def unload_weights(self, layer_id: int):
+        self._check(self._L.lutamm_unload_weights(self._h, layer_id))
+        self.layers.pop(layer_id, None)
+
+    # -- the operator (names follow the reference)
+    def amm_host(self, layer_id: int, input_tensor, output_tensor, n_tokens: int | None = None, flags: int = 0):
+        """amm_host() of the reference (src/host/amm_host.cpp:10-30)."""
+        M = int(n_tokens if n_tokens is not None else input_tensor.shape[0])
+        self._check(self._L.lutamm_amm(self._h, layer_id, _ptr(input_tensor), _ptr(output_tensor), M, flags))
+
+    def amm_debug(self, layer_id: int, x: np.ndarray, flags: int = 0):
+        """Host-array convenience for parity checks: returns (out fp32, idx uint8, acc int32)."""
+        info = self.layers[layer_id]
+        M = x.shape[0]
+        out = np.zeros((M, info.N), dtype=np.float32)
+        idx = np.zeros((M, info.CB), dtype=np.uint8)
+        acc = np.zeros((M, info.N), dtype=np.int32)
+        self._check(self._L.lutamm_amm_debug(self._h, layer_id, _ptr(x), _ptr(out), M, _ptr(idx), _ptr(acc), flags))
+        return out, idx, acc
+
+    def index_calculation(self, layer_id: int, input_tensor, index_out, n_tokens: int | None = None,
+                          index_format: int = INDEX_U8_ROWMAJOR):
+        """index_calculation() of the reference (src/host/index_calc_host.cpp:8-53)."""
+        M = int(n_tokens if n_tokens is not None else input_tensor.shape[0])
+        self._check(self._L.lutamm_index_calculation(self._h, layer_id, _ptr(input_tensor), _ptr(index_out), M,
+                                                     index_format))
+
+    def pim_lut(self, layer_id: int, input_index, output_tensor, n_tokens: int | None = None, flags: int = 0):
+        """pim_lut() of the reference (src/host/pim_lut_host.cpp:121-222)."""
+        M = int(n_tokens if n_tokens is not None else input_index.shape[0])
+        self._check(self._L.lutamm_pim_lut(self._h, layer_id, _ptr(input_index), _ptr(output_tensor), M, flags))
+
+    # -- plans / tuning / timing
+    def set_plan(self, layer_id: int, **kw):
+        p = Plan()
+        for k, v in kw.items():
+            setattr(p, k, v)
+        self._check(self._L.lutamm_set_plan(self._h, layer_id, ctypes.byref(p)))
+
+    def get_plan(self, layer_id: int) -> dict:
+        p = Plan()
+        self._check(self._L.lutamm_get_plan(self._h, layer_id, ctypes.byref(p)))
+        return p.as_dict()
+
+    def tune(self, layer_id: int, n_tokens: int) -> dict:
+        p = Plan()
+        self._check(self._L.lutamm_tune(self._h, layer_id, n_tokens, ctypes.byref(p)))
+        return p.as_dict()
+
+    def enable_timing(self, on: bool = True):
+        self._check(self._L.lutamm_enable_timing(self._h, 1 if on else 0))
+
+    def timings(self) -> dict:
+        t = Timings()
+        self._check(self._L.lutamm_get_timings(self._h, ctypes.byref(t)))
+        return {k: getattr(t, k) for k, _ in Timings._fields_}

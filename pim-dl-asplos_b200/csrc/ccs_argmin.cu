@@ -1,0 +1,271 @@
+// Step 1 of the AMM: closest-centroid search (CCS).
+//
+// Replaces index_calculation() of the reference (inference-engine/src/host/index_calc_host.cpp:8-53).
+// The result has to match that function bit for bit, which pins three things:
+//   * every fp32 operation rounds on its own (the reference is built for baseline x86-64,
+//     no FMA): __fsub_rn / __fmul_rn / __fadd_rn are never contracted by nvcc;
+//   * the squared distance accumulates in dimension order starting from 0;
+//   * the "argmin" is a sequential scan with hysteresis - centroid c replaces the running
+//     minimum only if fl(min - dist[c]) > 1e-6 - so it is order dependent and each
+//     (token, codebook) scan runs in one thread, centroids 0..CT-1 in order.  A tree or
+//     shuffle reduction gives different indices on near-ties.
+//
+// Two mappings:
+//   reg path    thread <-> codebook, centroids of that codebook live in registers, the
+//               thread walks a run of tokens; activations load as coalesced float2/float4.
+//               Used when CT*v <= 64 (all v in {2,4,8} x CT in {8,16,32} points with
+//               CT*v <= 64).
+//   smem path   thread <-> token, centroids of a block of codebooks sit in shared memory
+//               and are read as warp-wide broadcasts; any v, any CT <= 256.
+//
+// HBM traffic: 4*M*K (activations) + 4*CB*CT*v (centroids) + M*CB (uint8 indices).
+#include "kernels.h"
+#include "../../include/lutamm.h"
+
+namespace lutamm {
+
+namespace {
+
+constexpr float kEps = 1e-6f;  // (double)diff > 1e-6  <=>  diff > 1e-6f for fp32 diff
+
+template <int V>
+struct XVec {
+    float f[V];
+};
+
+template <int V>
+__device__ __forceinline__ void load_x(const float* __restrict__ p, float (&f)[V]) {
+    if constexpr (V % 4 == 0) {
+#pragma unroll
+        for (int i = 0; i < V / 4; ++i) {
+            float4 t = __ldg(reinterpret_cast<const float4*>(p) + i);
+            f[4 * i + 0] = t.x; f[4 * i + 1] = t.y; f[4 * i + 2] = t.z; f[4 * i + 3] = t.w;
+        }
+    } else if constexpr (V % 2 == 0) {
+#pragma unroll
+        for (int i = 0; i < V / 2; ++i) {
+            float2 t = __ldg(reinterpret_cast<const float2*>(p) + i);
+            f[2 * i + 0] = t.x; f[2 * i + 1] = t.y;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < V; ++i) f[i] = __ldg(p + i);
+    }
+}
+
+__device__ __forceinline__ size_t tiled_index_offset(uint32_t m, uint32_t cb, uint32_t CB, uint32_t n_stile,
+                                                     uint32_t cb_mtile) {
+    // index_calc_host.cpp:41-49
+    uint32_t n_tile = m / n_stile, n_in = m % n_stile;
+    uint32_t cb_tile = cb / cb_mtile, cb_in = cb % cb_mtile;
+    return (size_t)n_tile * n_stile * CB + (size_t)cb_tile * n_stile * cb_mtile + (size_t)n_in * cb_mtile + cb_in;
+}
+
+// ------------------------------------------------------------------ reg path
+constexpr int kRegThreads = 128;
+
+template <int V, int CT, bool TILED>
+__global__ void __launch_bounds__(kRegThreads)
+ccs_reg_kernel(const float* __restrict__ x, const float* __restrict__ cent, void* __restrict__ out, uint32_t M,
+               uint32_t K, uint32_t CB, uint32_t tokens_per_cta, uint32_t n_stile, uint32_t cb_mtile) {
+    const uint32_t cb = blockIdx.x * kRegThreads + threadIdx.x;
+    if (cb >= CB) return;
+    const uint32_t m0 = blockIdx.y * tokens_per_cta;
+    const uint32_t m1 = min(M, m0 + tokens_per_cta);
+
+    float c[CT][V];
+    {
+        const float* cp = cent + (size_t)cb * CT * V;
+#pragma unroll
+        for (int ct = 0; ct < CT; ++ct) {
+            float t[V];
+            load_x<V>(cp + ct * V, t);
+#pragma unroll
+            for (int d = 0; d < V; ++d) c[ct][d] = t[d];
+        }
+    }
+
+    const float* xp = x + (size_t)m0 * K + (size_t)cb * V;
+#pragma unroll 2
+    for (uint32_t m = m0; m < m1; ++m, xp += K) {
+        float xs[V];
+        load_x<V>(xp, xs);
+        float mn = 0.f;
+        uint32_t best = 0;
+#pragma unroll
+        for (int ct = 0; ct < CT; ++ct) {
+            float t = 0.f;
+#pragma unroll
+            for (int d = 0; d < V; ++d) {
+                float e = __fsub_rn(xs[d], c[ct][d]);
+                t = __fadd_rn(t, __fmul_rn(e, e));
+            }
+            if (ct == 0) {
+                mn = t;
+            } else {
+                bool take = __fsub_rn(mn, t) > kEps;  // false for NaN: keeps the earlier index
+                mn = take ? t : mn;
+                best = take ? (uint32_t)ct : best;
+            }
+        }
+        if constexpr (TILED) {
+            reinterpret_cast<uint16_t*>(out)[tiled_index_offset(m, cb, CB, n_stile, cb_mtile)] = (uint16_t)best;
+        } else {
+            reinterpret_cast<uint8_t*>(out)[(size_t)m * CB + cb] = (uint8_t)best;
+        }
+    }
+}
+
+// ------------------------------------------------------------------ smem path
+constexpr int kSmemThreads = 128;  // tokens per CTA
+
+// V > 0: compile-time sub-vector length, the token's slice sits in registers.
+// V == 0: run-time length, the slice is re-read (L1 resident) per centroid.
+template <int V, bool TILED>
+__global__ void __launch_bounds__(kSmemThreads)
+ccs_smem_kernel(const float* __restrict__ x, const float* __restrict__ cent, void* __restrict__ out, uint32_t M,
+                uint32_t K, uint32_t v_rt, uint32_t CB, uint32_t CT, uint32_t cb_per_cta, uint32_t n_stile,
+                uint32_t cb_mtile) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const uint32_t v = V > 0 ? (uint32_t)V : v_rt;
+    float* s_cent = reinterpret_cast<float*>(smem_raw);                   // [cbs][CT][v]
+    const uint32_t cb0 = blockIdx.x * cb_per_cta;
+    const uint32_t cbs = min(cb_per_cta, CB - cb0);
+    uint8_t* s_idx = smem_raw + (size_t)cb_per_cta * CT * v * sizeof(float);  // [128][cb_per_cta]
+
+    const uint32_t n_c = cbs * CT * v;
+    const float* gc = cent + (size_t)cb0 * CT * v;
+    for (uint32_t i = threadIdx.x; i < n_c; i += kSmemThreads) s_cent[i] = __ldg(gc + i);
+    __syncthreads();
+
+    const uint32_t m_base = blockIdx.y * kSmemThreads;
+    const uint32_t m = m_base + threadIdx.x;
+    if (m < M) {
+        const float* xp = x + (size_t)m * K + (size_t)cb0 * v;
+        for (uint32_t cl = 0; cl < cbs; ++cl, xp += v) {
+            const float* cp = s_cent + (size_t)cl * CT * v;
+            float mn = 0.f;
+            uint32_t best = 0;
+            if constexpr (V > 0) {
+                float xs[V > 0 ? V : 1];
+                load_x<(V > 0 ? V : 1)>(xp, xs);
+                for (uint32_t ct = 0; ct < CT; ++ct) {
+                    float t = 0.f;
+#pragma unroll
+                    for (int d = 0; d < V; ++d) {
+                        float e = __fsub_rn(xs[d], cp[ct * V + d]);
+                        t = __fadd_rn(t, __fmul_rn(e, e));
+                    }
+                    bool take = (ct > 0) && (__fsub_rn(mn, t) > kEps);
+                    if (ct == 0) mn = t;
+                    mn = take ? t : mn;
+                    best = take ? ct : best;
+                }
+            } else {
+                for (uint32_t ct = 0; ct < CT; ++ct) {
+                    float t = 0.f;
+                    for (uint32_t d = 0; d < v; ++d) {
+                        float e = __fsub_rn(__ldg(xp + d), cp[ct * v + d]);
+                        t = __fadd_rn(t, __fmul_rn(e, e));
+                    }
+                    bool take = (ct > 0) && (__fsub_rn(mn, t) > kEps);
+                    if (ct == 0) mn = t;
+                    mn = take ? t : mn;
+                    best = take ? ct : best;
+                }
+            }
+            s_idx[threadIdx.x * cb_per_cta + cl] = (uint8_t)best;
+        }
+    }
+    __syncthreads();
+    // write-out: consecutive threads -> consecutive codebooks of one token
+    const uint32_t rows = min((uint32_t)kSmemThreads, M > m_base ? M - m_base : 0u);
+    for (uint32_t i = threadIdx.x; i < rows * cbs; i += kSmemThreads) {
+        uint32_t r = i / cbs, cl = i % cbs;
+        uint8_t b = s_idx[r * cb_per_cta + cl];
+        if constexpr (TILED) {
+            reinterpret_cast<uint16_t*>(out)[tiled_index_offset(m_base + r, cb0 + cl, CB, n_stile, cb_mtile)] = b;
+        } else {
+            reinterpret_cast<uint8_t*>(out)[(size_t)(m_base + r) * CB + cb0 + cl] = b;
+        }
+    }
+}
+
+template <int V, int CT>
+cudaError_t run_reg(const CcsArgs& a, cudaStream_t s) {
+    uint32_t tpt = a.tokens_per_thread ? a.tokens_per_thread : 16u;
+    dim3 grid((a.CB + kRegThreads - 1) / kRegThreads, (a.M + tpt - 1) / tpt);
+    if (a.format == LUTAMM_INDEX_U16_TILED)
+        ccs_reg_kernel<V, CT, true><<<grid, kRegThreads, 0, s>>>(a.x, a.centroid, a.idx_out, a.M, a.K, a.CB, tpt,
+                                                                   a.n_stile, a.cb_mtile);
+    else
+        ccs_reg_kernel<V, CT, false><<<grid, kRegThreads, 0, s>>>(a.x, a.centroid, a.idx_out, a.M, a.K, a.CB, tpt,
+                                                                    a.n_stile, a.cb_mtile);
+    return cudaGetLastError();
+}
+
+template <int V>
+cudaError_t run_smem(const CcsArgs& a, cudaStream_t s) {
+    // centroid tile + index tile per CTA; keep under ~96 KB so two CTAs fit an SM
+    const size_t per_cb = (size_t)a.CT * a.v * sizeof(float) + kSmemThreads;
+    uint32_t cb_per_cta = (uint32_t)((96 * 1024) / per_cb);
+    if (cb_per_cta == 0) cb_per_cta = 1;
+    if (cb_per_cta > 64) cb_per_cta = 64;
+    if (cb_per_cta > a.CB) cb_per_cta = a.CB;
+    const size_t smem = per_cb * cb_per_cta;
+    if (smem > 200 * 1024) return cudaErrorInvalidValue;
+    dim3 grid((a.CB + cb_per_cta - 1) / cb_per_cta, (a.M + kSmemThreads - 1) / kSmemThreads);
+    cudaError_t e;
+    if (a.format == LUTAMM_INDEX_U16_TILED) {
+        auto k = ccs_smem_kernel<V, true>;
+        e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        k<<<grid, kSmemThreads, smem, s>>>(a.x, a.centroid, a.idx_out, a.M, a.K, a.v, a.CB, a.CT, cb_per_cta,
+                                           a.n_stile, a.cb_mtile);
+    } else {
+        auto k = ccs_smem_kernel<V, false>;
+        e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        k<<<grid, kSmemThreads, smem, s>>>(a.x, a.centroid, a.idx_out, a.M, a.K, a.v, a.CB, a.CT, cb_per_cta,
+                                           a.n_stile, a.cb_mtile);
+    }
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_ccs(const CcsArgs& a, cudaStream_t s, const char** why) {
+    *why = nullptr;
+    if (a.M == 0 || a.CB == 0) return cudaSuccess;
+    if (a.CT == 0 || a.CT > 256 || a.v == 0 || a.K != a.CB * a.v) {
+        *why = "closest-centroid search: need 1 <= num_centroid <= 256 and input_feature_len == num_codebook*sub_vec_len";
+        return cudaErrorInvalidValue;
+    }
+    // vector loads need the row pitch and the base address aligned to the vector width
+    const uintptr_t xa = reinterpret_cast<uintptr_t>(a.x), ca = reinterpret_cast<uintptr_t>(a.centroid);
+    const uint32_t vec_bytes = (a.v % 4 == 0) ? 16u : (a.v % 2 == 0) ? 8u : 4u;
+    const bool aligned = (xa % vec_bytes == 0) && (ca % vec_bytes == 0);
+    if (aligned) {
+#define LUTAMM_CCS_REG(V_, CT_) \
+    if (a.v == V_ && a.CT == CT_) return run_reg<V_, CT_>(a, s);
+        LUTAMM_CCS_REG(2, 8)
+        LUTAMM_CCS_REG(2, 16)
+        LUTAMM_CCS_REG(2, 32)
+        LUTAMM_CCS_REG(4, 8)
+        LUTAMM_CCS_REG(4, 16)
+        LUTAMM_CCS_REG(8, 8)
+#undef LUTAMM_CCS_REG
+        switch (a.v) {
+            case 1: return run_smem<1>(a, s);
+            case 2: return run_smem<2>(a, s);
+            case 4: return run_smem<4>(a, s);
+            case 8: return run_smem<8>(a, s);
+            case 16: return run_smem<16>(a, s);
+            case 32: return run_smem<32>(a, s);
+            default: break;
+        }
+    }
+    return run_smem<0>(a, s);
+}
+
+}  // namespace lutamm

@@ -1,0 +1,74 @@
+// Internal launcher interface between the C ABI (lutamm_capi.cu) and the kernels.
+#pragma once
+#include <cstdint>
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+namespace lutamm {
+
+// ---- step 1: closest-centroid search -------------------------------------------------
+struct CcsArgs {
+    const float* x;         // [M][K]
+    const float* centroid;  // [CB][CT][v]
+    void* idx_out;          // uint8 [M][CB] or uint16 tiled
+    uint32_t M, K, v, CB, CT;
+    uint32_t format;        // LUTAMM_INDEX_*
+    uint32_t n_stile, cb_mtile;  // tiled format only
+    uint32_t tokens_per_thread;  // 0 = default
+};
+cudaError_t launch_ccs(const CcsArgs& a, cudaStream_t s, const char** why);
+
+// ---- step 2+3: gather-accumulate + dequantise -----------------------------------------
+// Output addressing: row-major [M][N], or the reference's DPU-tiled layout.
+struct OutLayout {
+    uint32_t tiled;  // 0 = row-major
+    uint32_t n_stile, f_stile, f_mtile, lut_par;
+};
+
+struct LutArgs {
+    const uint8_t* idx;   // [M][CB]
+    const float* bias;    // [N]
+    float* out;           // fp32, layout per `layout`
+    int32_t* acc_out;     // optional int32 [M][N] row-major (parity checks), may be null
+    uint32_t M, CB, CT, N;
+    float scale, lut_bias;
+    OutLayout layout;
+};
+
+// Gather variant: LUT canonical [CB][CT][N] staged by 3-D TMA tiles.
+struct GatherPlan {
+    uint32_t cfg;  // tile configuration id
+};
+uint32_t gather_num_cfgs();
+// Encodes the tensor map the configuration needs (box sizes depend on it).
+cudaError_t gather_make_tmap(CUtensorMap* out, const int8_t* lut, uint32_t CB, uint32_t CT, uint32_t N, uint32_t cfg,
+                             const char** why);
+cudaError_t launch_gather(const LutArgs& a, const CUtensorMap& lut_map, uint32_t cfg, uint32_t* dev_err,
+                          cudaStream_t s, const char** why);
+
+// tcgen05 variant: LUT transposed to K-major [N][CB*CT] at load time, 2-D TMA tiles with
+// 128-byte swizzle; the one-hot operand is synthesised in shared memory from the indices.
+struct UmmaPlan {
+    uint32_t n_tile;  // 64 / 128 / 256
+    uint32_t split;   // CTAs sharing one output tile along the codebook axis
+    uint32_t stages;
+};
+bool umma_supported(uint32_t CB, uint32_t CT, uint32_t N);
+cudaError_t umma_make_tmap(CUtensorMap* out, const int8_t* lut_t, uint32_t CB, uint32_t CT, uint32_t N,
+                           uint32_t n_tile, const char** why);
+// `acc_scratch` (int32 [M][N]) and `tile_counters` are needed when split > 1.
+cudaError_t launch_umma(const LutArgs& a, const CUtensorMap& lut_t_map, const UmmaPlan& p, int32_t* acc_scratch,
+                        uint32_t* tile_counters, uint32_t* dev_err, cudaStream_t s, const char** why);
+void umma_default_plan(uint32_t M, uint32_t CB, uint32_t CT, uint32_t N, int sm_count, UmmaPlan* p);
+
+// LUT [CB*CT][N] -> [N][CB*CT]
+cudaError_t launch_transpose_lut(const int8_t* lut, int8_t* lut_t, uint32_t rows, uint32_t cols, cudaStream_t s);
+
+// Driver entry point for tensor-map encoding, resolved through the runtime so the library
+// carries no link-time dependency on the driver and loads on machines without one.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn get_encode_tiled();
+
+}  // namespace lutamm

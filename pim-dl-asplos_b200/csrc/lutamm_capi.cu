@@ -1,0 +1,678 @@
+// C ABI of the library (declared in include/lutamm.h): context, resident weights, the AMM
+// operator and its two halves, plans, tuning and timing.  Everything below this file is
+// CUDA for sm_100a; there is no CPU implementation of the operator in the library, so a
+// machine without a usable device gets an error from lutamm_create, never a slow answer.
+#include "../../include/lutamm.h"
+#include "kernels.h"
+
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <new>
+#include <string>
+#include <vector>
+
+using namespace lutamm;
+
+namespace lutamm {
+
+EncodeTiledFn get_encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+}  // namespace lutamm
+
+namespace {
+
+constexpr int kNumUmmaTiles = 3;  // 64, 128, 256
+inline int umma_tile_slot(uint32_t n_tile) { return n_tile == 64 ? 0 : n_tile == 128 ? 1 : 2; }
+
+struct Layer {
+    lutamm_index_params ip{};
+    lutamm_lut_params lp{};
+    uint32_t K = 0, v = 0, CB = 0, CT = 0, N = 0;
+    float* d_centroid = nullptr;
+    int8_t* d_lut = nullptr;    // canonical [CB][CT][N]
+    int8_t* d_lut_t = nullptr;  // [N][CB*CT], made on first use of the tcgen05 variant
+    float* d_bias = nullptr;
+    lutamm_plan plan{};
+    std::vector<CUtensorMap> gather_maps;
+    std::vector<char> gather_map_ok;
+    CUtensorMap umma_maps[kNumUmmaTiles];
+    bool umma_map_ok[kNumUmmaTiles] = {false, false, false};
+};
+
+struct Buf {
+    void* p = nullptr;
+    size_t cap = 0;
+};
+
+}  // namespace
+
+struct lutamm_ctx {
+    int device = 0;
+    int sm_count = 148;
+    cudaStream_t own_stream = nullptr;
+    cudaStream_t stream = nullptr;
+    std::map<int, Layer> layers;
+    Buf d_in, d_out, d_idx, d_idx16, d_acc_dbg, d_acc_scratch, d_counters;
+    uint32_t* d_err = nullptr;
+    uint32_t* h_err = nullptr;  // pinned
+    bool timing = false;
+    cudaEvent_t ev[6] = {};
+    lutamm_timings last{};
+    bool last_valid = false;
+    uint64_t launches = 0;
+    std::string err;
+};
+
+namespace {
+
+thread_local std::string g_noctx_err;
+
+int fail(lutamm_ctx* c, int code, const std::string& msg) {
+    if (c) c->err = msg; else g_noctx_err = msg;
+    return code;
+}
+
+#define CU_TRY(c, expr)                                                                              \
+    do {                                                                                             \
+        cudaError_t e__ = (expr);                                                                    \
+        if (e__ != cudaSuccess)                                                                      \
+            return fail((c), LUTAMM_ECUDA, std::string(#expr) + ": " + cudaGetErrorString(e__));      \
+    } while (0)
+
+struct DeviceGuard {
+    int prev = -1;
+    bool ok = false;
+    explicit DeviceGuard(int dev) {
+        if (cudaGetDevice(&prev) == cudaSuccess && cudaSetDevice(dev) == cudaSuccess) ok = true;
+    }
+    ~DeviceGuard() {
+        if (ok && prev >= 0) cudaSetDevice(prev);
+    }
+};
+
+// grow-only device buffer; `zero` clears newly allocated memory
+int ensure(lutamm_ctx* c, Buf& b, size_t bytes, bool zero = false) {
+    if (bytes <= b.cap) return LUTAMM_OK;
+    // Stream order: everything queued so far may still use the old block.
+    CU_TRY(c, cudaStreamSynchronize(c->stream));
+    if (b.p) CU_TRY(c, cudaFree(b.p));
+    b.p = nullptr;
+    b.cap = 0;
+    size_t want = bytes + bytes / 4 + 256;
+    cudaError_t e = cudaMalloc(&b.p, want);
+    if (e != cudaSuccess) {
+        want = bytes;
+        e = cudaMalloc(&b.p, want);
+    }
+    if (e != cudaSuccess) return fail(c, LUTAMM_ENOMEM, std::string("cudaMalloc: ") + cudaGetErrorString(e));
+    b.cap = want;
+    if (zero) CU_TRY(c, cudaMemsetAsync(b.p, 0, want, c->stream));
+    return LUTAMM_OK;
+}
+
+bool is_device_ptr(const void* p) {
+    cudaPointerAttributes at;
+    if (cudaPointerGetAttributes(&at, p) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    return at.type == cudaMemoryTypeDevice || at.type == cudaMemoryTypeManaged;
+}
+
+Layer* find_layer(lutamm_ctx* c, int id) {
+    auto it = c->layers.find(id);
+    return it == c->layers.end() ? nullptr : &it->second;
+}
+
+void free_layer(Layer& L) {
+    cudaFree(L.d_centroid);
+    cudaFree(L.d_lut);
+    cudaFree(L.d_lut_t);
+    cudaFree(L.d_bias);
+    L = Layer{};
+}
+
+uint32_t resolve_variant(const lutamm_ctx* c, const Layer& L) {
+    (void)c;
+    uint32_t v = L.plan.variant;
+    if (v == LUTAMM_VARIANT_AUTO) v = umma_supported(L.CB, L.CT, L.N) ? LUTAMM_VARIANT_UMMA : LUTAMM_VARIANT_GATHER;
+    return v;
+}
+
+OutLayout make_layout(const Layer& L, uint32_t flags) {
+    OutLayout o{};
+    if (flags & LUTAMM_FLAG_OUTPUT_TILED) {
+        o.tiled = 1;
+        o.n_stile = L.lp.n_stile_size;
+        o.f_stile = L.lp.feature_stile_size;
+        o.f_mtile = L.lp.feature_mtile_size;
+        o.lut_par = L.lp.lut_parallelism ? L.lp.lut_parallelism : (L.lp.feature_stile_size ? L.N / L.lp.feature_stile_size : 1);
+    }
+    return o;
+}
+
+int check_tiled(lutamm_ctx* c, const Layer& L, uint32_t M) {
+    const lutamm_lut_params& p = L.lp;
+    if (!p.n_stile_size || !p.feature_stile_size || !p.feature_mtile_size || M % p.n_stile_size ||
+        L.N % p.feature_stile_size || p.feature_stile_size % p.feature_mtile_size)
+        return fail(c, LUTAMM_EINVAL,
+                    "tiled output needs n % n_stile_size == 0, output_feature_len % feature_stile_size == 0 and "
+                    "feature_stile_size % feature_mtile_size == 0 (parser.cpp:61-63)");
+    return LUTAMM_OK;
+}
+
+// step 2+3 on device buffers
+int run_lut(lutamm_ctx* c, Layer& L, const uint8_t* d_idx, float* d_out, int32_t* d_acc_out, uint32_t M,
+            uint32_t flags, const lutamm_plan& plan) {
+    LutArgs a{};
+    a.idx = d_idx;
+    a.bias = L.d_bias;
+    a.out = d_out;
+    a.acc_out = d_acc_out;
+    a.M = M; a.CB = L.CB; a.CT = L.CT; a.N = L.N;
+    a.scale = L.lp.scale;
+    a.lut_bias = L.lp.bias;
+    a.layout = make_layout(L, flags);
+    const char* why = nullptr;
+    uint32_t variant = plan.variant;
+    if (variant == LUTAMM_VARIANT_AUTO) variant = resolve_variant(c, L);
+    if (variant == LUTAMM_VARIANT_UMMA) {
+        if (!umma_supported(L.CB, L.CT, L.N))
+            return fail(c, LUTAMM_EUNSUPPORTED, "tcgen05 variant does not cover this shape (num_centroid must be a power of two in 8..256)");
+        UmmaPlan up;
+        umma_default_plan(M, L.CB, L.CT, L.N, c->sm_count, &up);
+        if (plan.umma_n_tile) up.n_tile = plan.umma_n_tile;
+        if (plan.umma_n_tile && !plan.umma_split) {
+            // recompute the split for the forced tile
+            UmmaPlan tmp = up;
+            const uint32_t tiles = ((M + 127) / 128) * ((L.N + up.n_tile - 1) / up.n_tile);
+            const uint32_t slabs = (uint32_t)(((uint64_t)L.CB * L.CT + 127) / 128);
+            uint32_t split = tiles < (uint32_t)c->sm_count ? (uint32_t)c->sm_count / tiles : 1;
+            const uint32_t max_split = slabs / 8 ? slabs / 8 : 1;
+            if (split > max_split) split = max_split;
+            if (split > 16) split = 16;
+            tmp.split = split ? split : 1;
+            tmp.stages = up.n_tile == 256 ? 4 : (up.n_tile == 128 ? 6 : 8);
+            up = tmp;
+        }
+        if (plan.umma_split) up.split = plan.umma_split;
+        if (plan.umma_stages) up.stages = plan.umma_stages;
+        if (up.n_tile != 64 && up.n_tile != 128 && up.n_tile != 256)
+            return fail(c, LUTAMM_EINVAL, "umma_n_tile must be 64, 128 or 256");
+        if (!L.d_lut_t) {
+            const size_t bytes = (size_t)L.CB * L.CT * L.N;
+            CU_TRY(c, cudaMalloc(&L.d_lut_t, bytes));
+            CU_TRY(c, launch_transpose_lut(L.d_lut, L.d_lut_t, L.CB * L.CT, L.N, c->stream));
+            ++c->launches;
+        }
+        const int slot = umma_tile_slot(up.n_tile);
+        if (!L.umma_map_ok[slot]) {
+            cudaError_t e = umma_make_tmap(&L.umma_maps[slot], L.d_lut_t, L.CB, L.CT, L.N, up.n_tile, &why);
+            if (e != cudaSuccess) return fail(c, LUTAMM_ECUDA, why ? why : cudaGetErrorString(e));
+            L.umma_map_ok[slot] = true;
+        }
+        if (up.split > 1) {
+            const uint32_t tiles = ((M + 127) / 128) * ((L.N + up.n_tile - 1) / up.n_tile);
+            int r = ensure(c, c->d_acc_scratch, (size_t)M * L.N * sizeof(int32_t), true);
+            if (r) return r;
+            r = ensure(c, c->d_counters, (size_t)tiles * sizeof(uint32_t), true);
+            if (r) return r;
+        }
+        cudaError_t e = launch_umma(a, L.umma_maps[slot], up, static_cast<int32_t*>(c->d_acc_scratch.p),
+                                    static_cast<uint32_t*>(c->d_counters.p), c->d_err, c->stream, &why);
+        if (e != cudaSuccess) return fail(c, LUTAMM_ECUDA, why ? why : (std::string("tcgen05 launch: ") + cudaGetErrorString(e)));
+        ++c->launches;
+        return LUTAMM_OK;
+    }
+    if (variant != LUTAMM_VARIANT_GATHER) return fail(c, LUTAMM_EINVAL, "unknown kernel variant");
+    uint32_t cfg = plan.gather_cfg;
+    if (cfg >= gather_num_cfgs()) return fail(c, LUTAMM_EINVAL, "unknown gather tile configuration");
+    if (L.gather_maps.size() != gather_num_cfgs()) {
+        L.gather_maps.resize(gather_num_cfgs());
+        L.gather_map_ok.assign(gather_num_cfgs(), 0);
+    }
+    if (!L.gather_map_ok[cfg]) {
+        cudaError_t e = gather_make_tmap(&L.gather_maps[cfg], L.d_lut, L.CB, L.CT, L.N, cfg, &why);
+        if (e != cudaSuccess) return fail(c, LUTAMM_ECUDA, why ? why : cudaGetErrorString(e));
+        L.gather_map_ok[cfg] = 1;
+    }
+    cudaError_t e = launch_gather(a, L.gather_maps[cfg], cfg, c->d_err, c->stream, &why);
+    if (e != cudaSuccess) return fail(c, LUTAMM_ECUDA, why ? why : (std::string("gather launch: ") + cudaGetErrorString(e)));
+    ++c->launches;
+    return LUTAMM_OK;
+}
+
+int run_ccs(lutamm_ctx* c, Layer& L, const float* d_x, void* d_idx, uint32_t M, uint32_t format) {
+    CcsArgs a{};
+    a.x = d_x;
+    a.centroid = L.d_centroid;
+    a.idx_out = d_idx;
+    a.M = M; a.K = L.K; a.v = L.v; a.CB = L.CB; a.CT = L.CT;
+    a.format = format;
+    a.n_stile = L.ip.n_stile_size;
+    a.cb_mtile = L.ip.cb_mtile_size;
+    a.tokens_per_thread = L.plan.ccs_tokens;
+    const char* why = nullptr;
+    cudaError_t e = launch_ccs(a, c->stream, &why);
+    if (e != cudaSuccess) return fail(c, LUTAMM_ECUDA, why ? why : (std::string("search launch: ") + cudaGetErrorString(e)));
+    ++c->launches;
+    return LUTAMM_OK;
+}
+
+// read back the device error word after a synchronisation
+int check_dev_err(lutamm_ctx* c) {
+    CU_TRY(c, cudaMemcpyAsync(c->h_err, c->d_err, sizeof(uint32_t), cudaMemcpyDeviceToHost, c->stream));
+    CU_TRY(c, cudaStreamSynchronize(c->stream));
+    if (*c->h_err) {
+        const uint32_t code = *c->h_err;
+        cudaMemsetAsync(c->d_err, 0, sizeof(uint32_t), c->stream);
+        return fail(c, LUTAMM_EDEVICE, "a kernel gave up on a bounded wait (code " + std::to_string(code) + "); output is not valid");
+    }
+    return LUTAMM_OK;
+}
+
+int amm_impl(lutamm_ctx* c, int layer_id, const float* input, float* output, uint32_t M, uint8_t* idx_out,
+             int32_t* acc_out, uint32_t flags) {
+    if (!c) return fail(nullptr, LUTAMM_EINVAL, "null context");
+    DeviceGuard g(c->device);
+    Layer* L = find_layer(c, layer_id);
+    if (!L) return fail(c, LUTAMM_ENOLAYER, "no weights loaded for layer " + std::to_string(layer_id));
+    if (M == 0) return LUTAMM_OK;
+    if (!input || !output) return fail(c, LUTAMM_EINVAL, "null input or output");
+    if ((flags & LUTAMM_FLAG_OUTPUT_TILED)) {
+        int r = check_tiled(c, *L, M);
+        if (r) return r;
+    }
+    const bool in_dev = is_device_ptr(input), out_dev = is_device_ptr(output);
+    if ((flags & LUTAMM_FLAG_ASYNC) && !(in_dev && out_dev && !idx_out && !acc_out))
+        return fail(c, LUTAMM_EINVAL, "LUTAMM_FLAG_ASYNC needs device input and output buffers and no debug outputs");
+    if (in_dev && (reinterpret_cast<uintptr_t>(input) & 3u)) return fail(c, LUTAMM_EINVAL, "input is not 4-byte aligned");
+    if (out_dev && (reinterpret_cast<uintptr_t>(output) & 15u)) return fail(c, LUTAMM_EINVAL, "device output must be 16-byte aligned");
+
+    const size_t in_bytes = (size_t)M * L->K * sizeof(float), out_bytes = (size_t)M * L->N * sizeof(float);
+    int r;
+    const float* d_x = input;
+    float* d_y = output;
+    const bool t = c->timing;
+    if (t) CU_TRY(c, cudaEventRecord(c->ev[0], c->stream));
+    if (!in_dev) {
+        if ((r = ensure(c, c->d_in, in_bytes))) return r;
+        CU_TRY(c, cudaMemcpyAsync(c->d_in.p, input, in_bytes, cudaMemcpyHostToDevice, c->stream));
+        d_x = static_cast<const float*>(c->d_in.p);
+    }
+    if (!out_dev) {
+        if ((r = ensure(c, c->d_out, out_bytes))) return r;
+        d_y = static_cast<float*>(c->d_out.p);
+    }
+    if ((r = ensure(c, c->d_idx, (size_t)M * L->CB))) return r;
+    int32_t* d_acc = nullptr;
+    if (acc_out) {
+        if ((r = ensure(c, c->d_acc_dbg, (size_t)M * L->N * sizeof(int32_t)))) return r;
+        d_acc = static_cast<int32_t*>(c->d_acc_dbg.p);
+    }
+    if (t) CU_TRY(c, cudaEventRecord(c->ev[1], c->stream));
+    if ((r = run_ccs(c, *L, d_x, c->d_idx.p, M, LUTAMM_INDEX_U8_ROWMAJOR))) return r;
+    if (t) CU_TRY(c, cudaEventRecord(c->ev[2], c->stream));
+    if ((r = run_lut(c, *L, static_cast<const uint8_t*>(c->d_idx.p), d_y, d_acc, M, flags, L->plan))) return r;
+    if (t) CU_TRY(c, cudaEventRecord(c->ev[3], c->stream));
+    if (!out_dev) CU_TRY(c, cudaMemcpyAsync(output, d_y, out_bytes, cudaMemcpyDeviceToHost, c->stream));
+    if (idx_out)
+        CU_TRY(c, cudaMemcpyAsync(idx_out, c->d_idx.p, (size_t)M * L->CB, cudaMemcpyDefault, c->stream));
+    if (acc_out)
+        CU_TRY(c, cudaMemcpyAsync(acc_out, d_acc, (size_t)M * L->N * sizeof(int32_t), cudaMemcpyDefault, c->stream));
+    if (t) CU_TRY(c, cudaEventRecord(c->ev[4], c->stream));
+    if (flags & LUTAMM_FLAG_ASYNC) return LUTAMM_OK;
+    if ((r = check_dev_err(c))) return r;
+    if (t) {
+        float a01 = 0, a12 = 0, a23 = 0, a34 = 0;
+        cudaEventElapsedTime(&a01, c->ev[0], c->ev[1]);
+        cudaEventElapsedTime(&a12, c->ev[1], c->ev[2]);
+        cudaEventElapsedTime(&a23, c->ev[2], c->ev[3]);
+        cudaEventElapsedTime(&a34, c->ev[3], c->ev[4]);
+        c->last.data_transfer_ms = a01 + a34;
+        c->last.index_calc_ms = a12;
+        c->last.lut_kernel_ms = a23;
+        c->last.total_ms = a01 + a12 + a23 + a34;
+        c->last_valid = true;
+    }
+    return LUTAMM_OK;
+}
+
+}  // namespace
+
+// =========================================================================== C ABI
+extern "C" {
+
+const char* lutamm_version(void) { return "lutamm-b200 0.1 (sm_100a)"; }
+
+int lutamm_create(lutamm_ctx** out, int device) {
+    if (!out) return fail(nullptr, LUTAMM_EINVAL, "null out pointer");
+    *out = nullptr;
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess || n == 0)
+        return fail(nullptr, LUTAMM_ECUDA, std::string("no usable CUDA device: ") + cudaGetErrorString(e));
+    if (device < 0 || device >= n) return fail(nullptr, LUTAMM_EINVAL, "device ordinal out of range");
+    cudaDeviceProp prop;
+    CU_TRY(nullptr, cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10)
+        return fail(nullptr, LUTAMM_EUNSUPPORTED, "this library is built for sm_100a (B200) only; found sm_" +
+                                                       std::to_string(prop.major) + std::to_string(prop.minor));
+    lutamm_ctx* c = new (std::nothrow) lutamm_ctx();
+    if (!c) return fail(nullptr, LUTAMM_ENOMEM, "out of host memory");
+    c->device = device;
+    c->sm_count = prop.multiProcessorCount;
+    DeviceGuard g(device);
+    if (cudaStreamCreateWithFlags(&c->own_stream, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaMalloc(&c->d_err, sizeof(uint32_t)) != cudaSuccess ||
+        cudaMemset(c->d_err, 0, sizeof(uint32_t)) != cudaSuccess ||
+        cudaMallocHost(&c->h_err, sizeof(uint32_t)) != cudaSuccess) {
+        std::string m = std::string("context set-up failed: ") + cudaGetErrorString(cudaGetLastError());
+        delete c;
+        return fail(nullptr, LUTAMM_ECUDA, m);
+    }
+    *c->h_err = 0;
+    c->stream = c->own_stream;
+    for (auto& ev : c->ev) cudaEventCreate(&ev);
+    *out = c;
+    return LUTAMM_OK;
+}
+
+int lutamm_destroy(lutamm_ctx* c) {
+    if (!c) return LUTAMM_OK;
+    DeviceGuard g(c->device);
+    cudaStreamSynchronize(c->stream);
+    for (auto& kv : c->layers) free_layer(kv.second);
+    for (Buf* b : {&c->d_in, &c->d_out, &c->d_idx, &c->d_idx16, &c->d_acc_dbg, &c->d_acc_scratch, &c->d_counters})
+        cudaFree(b->p);
+    cudaFree(c->d_err);
+    cudaFreeHost(c->h_err);
+    for (auto& ev : c->ev)
+        if (ev) cudaEventDestroy(ev);
+    if (c->own_stream) cudaStreamDestroy(c->own_stream);
+    delete c;
+    return LUTAMM_OK;
+}
+
+int lutamm_set_stream(lutamm_ctx* c, void* cuda_stream) {
+    if (!c) return fail(nullptr, LUTAMM_EINVAL, "null context");
+    DeviceGuard g(c->device);
+    CU_TRY(c, cudaStreamSynchronize(c->stream));
+    c->stream = cuda_stream ? static_cast<cudaStream_t>(cuda_stream) : c->own_stream;
+    return LUTAMM_OK;
+}
+
+int lutamm_sync(lutamm_ctx* c) {
+    if (!c) return fail(nullptr, LUTAMM_EINVAL, "null context");
+    DeviceGuard g(c->device);
+    return check_dev_err(c);
+}
+
+const char* lutamm_last_error(const lutamm_ctx* c) { return c ? c->err.c_str() : g_noctx_err.c_str(); }
+
+int lutamm_load_weights(lutamm_ctx* c, int layer_id, const float* centroid, const int8_t* lut, const float* bias,
+                        const lutamm_index_params* ip, const lutamm_lut_params* lp) {
+    if (!c) return fail(nullptr, LUTAMM_EINVAL, "null context");
+    if (!centroid || !lut || !bias || !ip || !lp) return fail(c, LUTAMM_EINVAL, "null argument");
+    const uint32_t K = ip->input_feature_len, CB = ip->num_codebook, CT = ip->num_centroid, N = lp->output_feature_len;
+    if (!K || !CB || !CT || !N) return fail(c, LUTAMM_EINVAL, "zero-sized shape parameter");
+    if (K % CB) return fail(c, LUTAMM_EINVAL, "input_feature_len % num_codebook != 0 (parser.cpp:57)");
+    const uint32_t v = K / CB;
+    if (ip->sub_vec_len && ip->sub_vec_len != v)
+        return fail(c, LUTAMM_EINVAL, "sub_vec_len != input_feature_len / num_codebook (parser.cpp:26)");
+    if (lp->num_codebook != CB || lp->num_centroid != CT)
+        return fail(c, LUTAMM_EINVAL, "index and LUT parameter blocks disagree on num_codebook / num_centroid");
+    if (CT > 256) return fail(c, LUTAMM_EINVAL, "num_centroid > 256 does not fit the uint8 index");
+    if (N % 16) return fail(c, LUTAMM_EINVAL, "output_feature_len must be a multiple of 16");
+    if ((uint64_t)CB * CT * N >= (1ull << 40)) return fail(c, LUTAMM_EINVAL, "LUT too large");
+    DeviceGuard g(c->device);
+    CU_TRY(c, cudaStreamSynchronize(c->stream));
+    Layer* old = find_layer(c, layer_id);
+    if (old) free_layer(*old);
+    Layer& L = c->layers[layer_id];
+    L.ip = *ip; L.lp = *lp;
+    L.K = K; L.v = v; L.CB = CB; L.CT = CT; L.N = N;
+    const size_t cb = (size_t)CB * CT * v * sizeof(float), lb = (size_t)CB * CT * N, bb = (size_t)N * sizeof(float);
+    cudaError_t e;
+    if ((e = cudaMalloc(&L.d_centroid, cb)) != cudaSuccess || (e = cudaMalloc(&L.d_lut, lb)) != cudaSuccess ||
+        (e = cudaMalloc(&L.d_bias, bb)) != cudaSuccess) {
+        free_layer(L);
+        c->layers.erase(layer_id);
+        return fail(c, LUTAMM_ENOMEM, std::string("cudaMalloc for weights: ") + cudaGetErrorString(e));
+    }
+    CU_TRY(c, cudaMemcpyAsync(L.d_centroid, centroid, cb, cudaMemcpyDefault, c->stream));
+    CU_TRY(c, cudaMemcpyAsync(L.d_lut, lut, lb, cudaMemcpyDefault, c->stream));
+    CU_TRY(c, cudaMemcpyAsync(L.d_bias, bias, bb, cudaMemcpyDefault, c->stream));
+    CU_TRY(c, cudaStreamSynchronize(c->stream));
+    L.plan = lutamm_plan{};
+    return LUTAMM_OK;
+}
+
+int lutamm_unload_weights(lutamm_ctx* c, int layer_id) {
+    if (!c) return fail(nullptr, LUTAMM_EINVAL, "null context");
+    DeviceGuard g(c->device);
+    Layer* L = find_layer(c, layer_id);
+    if (!L) return fail(c, LUTAMM_ENOLAYER, "no weights loaded for layer " + std::to_string(layer_id));
+    CU_TRY(c, cudaStreamSynchronize(c->stream));
+    free_layer(*L);
+    c->layers.erase(layer_id);
+    return LUTAMM_OK;
+}
+
+int lutamm_amm(lutamm_ctx* c, int layer_id, const float* input, float* output, uint32_t n_tokens, uint32_t flags) {
+    return amm_impl(c, layer_id, input, output, n_tokens, nullptr, nullptr, flags);
+}
+
+int lutamm_amm_debug(lutamm_ctx* c, int layer_id, const float* input, float* output, uint32_t n_tokens,
+                     uint8_t* idx_out, int32_t* acc_out, uint32_t flags) {
+    return amm_impl(c, layer_id, input, output, n_tokens, idx_out, acc_out, flags & ~LUTAMM_FLAG_ASYNC);
+}
+
+int lutamm_index_calculation(lutamm_ctx* c, int layer_id, const float* input, void* index_out, uint32_t M,
+                             uint32_t format) {
+    if (!c) return fail(nullptr, LUTAMM_EINVAL, "null context");
+    DeviceGuard g(c->device);
+    Layer* L = find_layer(c, layer_id);
+    if (!L) return fail(c, LUTAMM_ENOLAYER, "no weights loaded for layer " + std::to_string(layer_id));
+    if (M == 0) return LUTAMM_OK;
+    if (!input || !index_out) return fail(c, LUTAMM_EINVAL, "null input or output");
+    if (format != LUTAMM_INDEX_U8_ROWMAJOR && format != LUTAMM_INDEX_U16_TILED)
+        return fail(c, LUTAMM_EINVAL, "unknown index format");
+    if (format == LUTAMM_INDEX_U16_TILED) {
+        if (!L->ip.n_stile_size || !L->ip.cb_mtile_size || M % L->ip.n_stile_size || L->CB % L->ip.cb_mtile_size)
+            return fail(c, LUTAMM_EINVAL, "tiled index layout needs n % n_stile_size == 0 and num_codebook % cb_mtile_size == 0");
+    }
+    int r;
+    const float* d_x = input;
+    if (!is_device_ptr(input)) {
+        const size_t in_bytes = (size_t)M * L->K * sizeof(float);
+        if ((r = ensure(c, c->d_in, in_bytes))) return r;
+        CU_TRY(c, cudaMemcpyAsync(c->d_in.p, input, in_bytes, cudaMemcpyHostToDevice, c->stream));
+        d_x = static_cast<const float*>(c->d_in.p);
+    }
+    const size_t esz = format == LUTAMM_INDEX_U16_TILED ? 2 : 1;
+    const size_t obytes = (size_t)M * L->CB * esz;
+    void* d_o = index_out;
+    const bool out_dev = is_device_ptr(index_out);
+    if (!out_dev) {
+        Buf& b = esz == 2 ? c->d_idx16 : c->d_idx;
+        if ((r = ensure(c, b, obytes))) return r;
+        d_o = b.p;
+    }
+    if ((r = run_ccs(c, *L, d_x, d_o, M, format))) return r;
+    if (!out_dev) CU_TRY(c, cudaMemcpyAsync(index_out, d_o, obytes, cudaMemcpyDeviceToHost, c->stream));
+    return check_dev_err(c);
+}
+
+int lutamm_pim_lut(lutamm_ctx* c, int layer_id, const uint8_t* index, float* output, uint32_t M, uint32_t flags) {
+    if (!c) return fail(nullptr, LUTAMM_EINVAL, "null context");
+    DeviceGuard g(c->device);
+    Layer* L = find_layer(c, layer_id);
+    if (!L) return fail(c, LUTAMM_ENOLAYER, "no weights loaded for layer " + std::to_string(layer_id));
+    if (M == 0) return LUTAMM_OK;
+    if (!index || !output) return fail(c, LUTAMM_EINVAL, "null index or output");
+    int r;
+    if ((flags & LUTAMM_FLAG_OUTPUT_TILED) && (r = check_tiled(c, *L, M))) return r;
+    const bool in_dev = is_device_ptr(index), out_dev = is_device_ptr(output);
+    if ((flags & LUTAMM_FLAG_ASYNC) && !(in_dev && out_dev))
+        return fail(c, LUTAMM_EINVAL, "LUTAMM_FLAG_ASYNC needs device buffers");
+    const uint8_t* d_i = index;
+    if (!in_dev) {
+        if ((r = ensure(c, c->d_idx, (size_t)M * L->CB))) return r;
+        CU_TRY(c, cudaMemcpyAsync(c->d_idx.p, index, (size_t)M * L->CB, cudaMemcpyHostToDevice, c->stream));
+        d_i = static_cast<const uint8_t*>(c->d_idx.p);
+    }
+    float* d_y = output;
+    const size_t out_bytes = (size_t)M * L->N * sizeof(float);
+    if (!out_dev) {
+        if ((r = ensure(c, c->d_out, out_bytes))) return r;
+        d_y = static_cast<float*>(c->d_out.p);
+    }
+    if ((r = run_lut(c, *L, d_i, d_y, nullptr, M, flags, L->plan))) return r;
+    if (!out_dev) CU_TRY(c, cudaMemcpyAsync(output, d_y, out_bytes, cudaMemcpyDeviceToHost, c->stream));
+    if (flags & LUTAMM_FLAG_ASYNC) return LUTAMM_OK;
+    return check_dev_err(c);
+}
+
+int lutamm_set_plan(lutamm_ctx* c, int layer_id, const lutamm_plan* plan) {
+    if (!c) return fail(nullptr, LUTAMM_EINVAL, "null context");
+    Layer* L = find_layer(c, layer_id);
+    if (!L) return fail(c, LUTAMM_ENOLAYER, "no weights loaded for layer " + std::to_string(layer_id));
+    if (!plan) return fail(c, LUTAMM_EINVAL, "null plan");
+    if (plan->variant > LUTAMM_VARIANT_UMMA) return fail(c, LUTAMM_EINVAL, "unknown kernel variant");
+    if (plan->gather_cfg >= gather_num_cfgs()) return fail(c, LUTAMM_EINVAL, "unknown gather tile configuration");
+    if (plan->umma_n_tile && plan->umma_n_tile != 64 && plan->umma_n_tile != 128 && plan->umma_n_tile != 256)
+        return fail(c, LUTAMM_EINVAL, "umma_n_tile must be 0, 64, 128 or 256");
+    if (plan->variant == LUTAMM_VARIANT_UMMA && !umma_supported(L->CB, L->CT, L->N))
+        return fail(c, LUTAMM_EUNSUPPORTED, "tcgen05 variant does not cover this shape");
+    L->plan = *plan;
+    return LUTAMM_OK;
+}
+
+int lutamm_get_plan(lutamm_ctx* c, int layer_id, lutamm_plan* plan) {
+    if (!c) return fail(nullptr, LUTAMM_EINVAL, "null context");
+    Layer* L = find_layer(c, layer_id);
+    if (!L) return fail(c, LUTAMM_ENOLAYER, "no weights loaded for layer " + std::to_string(layer_id));
+    if (!plan) return fail(c, LUTAMM_EINVAL, "null plan");
+    *plan = L->plan;
+    return LUTAMM_OK;
+}
+
+int lutamm_tune(lutamm_ctx* c, int layer_id, uint32_t M, lutamm_plan* best_out) {
+    if (!c) return fail(nullptr, LUTAMM_EINVAL, "null context");
+    DeviceGuard g(c->device);
+    Layer* L = find_layer(c, layer_id);
+    if (!L) return fail(c, LUTAMM_ENOLAYER, "no weights loaded for layer " + std::to_string(layer_id));
+    if (M == 0) return fail(c, LUTAMM_EINVAL, "cannot tune for zero tokens");
+    int r;
+    // Inputs: zero activations give valid indices; the kernels' timing does not depend on values.
+    if ((r = ensure(c, c->d_in, (size_t)M * L->K * sizeof(float)))) return r;
+    if ((r = ensure(c, c->d_out, (size_t)M * L->N * sizeof(float)))) return r;
+    if ((r = ensure(c, c->d_idx, (size_t)M * L->CB))) return r;
+    CU_TRY(c, cudaMemsetAsync(c->d_in.p, 0, (size_t)M * L->K * sizeof(float), c->stream));
+
+    std::vector<lutamm_plan> cands;
+    for (uint32_t cfg = 0; cfg < gather_num_cfgs(); ++cfg) {
+        lutamm_plan p{};
+        p.variant = LUTAMM_VARIANT_GATHER;
+        p.gather_cfg = cfg;
+        cands.push_back(p);
+    }
+    if (umma_supported(L->CB, L->CT, L->N)) {
+        const uint32_t slabs = (uint32_t)(((uint64_t)L->CB * L->CT + 127) / 128);
+        for (uint32_t nt : {128u, 256u}) {
+            if (nt > 128 && L->N < 256) continue;
+            const uint32_t tiles = ((M + 127) / 128) * ((L->N + nt - 1) / nt);
+            std::vector<uint32_t> splits = {1};
+            uint32_t s_fill = tiles < (uint32_t)c->sm_count ? (uint32_t)c->sm_count / tiles : 1;
+            for (uint32_t s : {s_fill, s_fill * 2, s_fill / 2})
+                if (s > 1 && s <= slabs / 2 && s <= 32) splits.push_back(s);
+            for (uint32_t s : splits) {
+                lutamm_plan p{};
+                p.variant = LUTAMM_VARIANT_UMMA;
+                p.umma_n_tile = nt;
+                p.umma_split = s;
+                cands.push_back(p);
+            }
+        }
+    }
+    // ccs tokens-per-thread candidates are searched after the LUT variant
+    cudaEvent_t e0 = c->ev[0], e1 = c->ev[1];
+    auto time_lut = [&](const lutamm_plan& p, float* ms) -> int {
+        int rr;
+        for (int w = 0; w < 2; ++w)
+            if ((rr = run_lut(c, *L, static_cast<const uint8_t*>(c->d_idx.p), static_cast<float*>(c->d_out.p), nullptr, M, 0, p))) return rr;
+        CU_TRY(c, cudaEventRecord(e0, c->stream));
+        const int reps = 5;
+        for (int i = 0; i < reps; ++i)
+            if ((rr = run_lut(c, *L, static_cast<const uint8_t*>(c->d_idx.p), static_cast<float*>(c->d_out.p), nullptr, M, 0, p))) return rr;
+        CU_TRY(c, cudaEventRecord(e1, c->stream));
+        if ((rr = check_dev_err(c))) return rr;
+        float t = 0;
+        CU_TRY(c, cudaEventElapsedTime(&t, e0, e1));
+        *ms = t / reps;
+        return LUTAMM_OK;
+    };
+    if ((r = run_ccs(c, *L, static_cast<const float*>(c->d_in.p), c->d_idx.p, M, LUTAMM_INDEX_U8_ROWMAJOR))) return r;
+    lutamm_plan best = L->plan;
+    float best_ms = 1e30f;
+    for (const lutamm_plan& p : cands) {
+        float ms = 0;
+        r = time_lut(p, &ms);
+        if (r == LUTAMM_EDEVICE) return r;
+        if (r) continue;  // a candidate the shape does not admit
+        if (ms < best_ms) { best_ms = ms; best = p; }
+    }
+    // search granularity of step 1
+    float best_ccs = 1e30f;
+    uint32_t best_tok = 0;
+    for (uint32_t tok : {4u, 8u, 16u, 32u, 64u}) {
+        L->plan.ccs_tokens = tok;
+        for (int w = 0; w < 2; ++w)
+            if ((r = run_ccs(c, *L, static_cast<const float*>(c->d_in.p), c->d_idx.p, M, LUTAMM_INDEX_U8_ROWMAJOR))) return r;
+        CU_TRY(c, cudaEventRecord(e0, c->stream));
+        for (int i = 0; i < 5; ++i)
+            if ((r = run_ccs(c, *L, static_cast<const float*>(c->d_in.p), c->d_idx.p, M, LUTAMM_INDEX_U8_ROWMAJOR))) return r;
+        CU_TRY(c, cudaEventRecord(e1, c->stream));
+        CU_TRY(c, cudaStreamSynchronize(c->stream));
+        float t = 0;
+        CU_TRY(c, cudaEventElapsedTime(&t, e0, e1));
+        if (t < best_ccs) { best_ccs = t; best_tok = tok; }
+    }
+    best.ccs_tokens = best_tok;
+    L->plan = best;
+    if (best_out) *best_out = best;
+    return LUTAMM_OK;
+}
+
+int lutamm_enable_timing(lutamm_ctx* c, int on) {
+    if (!c) return fail(nullptr, LUTAMM_EINVAL, "null context");
+    c->timing = on != 0;
+    c->last_valid = false;
+    return LUTAMM_OK;
+}
+
+int lutamm_get_timings(lutamm_ctx* c, lutamm_timings* out) {
+    if (!c) return fail(nullptr, LUTAMM_EINVAL, "null context");
+    if (!out) return fail(c, LUTAMM_EINVAL, "null out pointer");
+    if (!c->last_valid) return fail(c, LUTAMM_EINVAL, "no timed call yet (lutamm_enable_timing, then a synchronous call)");
+    *out = c->last;
+    return LUTAMM_OK;
+}
+
+uint64_t lutamm_launch_count(const lutamm_ctx* c) { return c ? c->launches : 0; }
+
+}  // extern "C"
