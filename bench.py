@@ -1,0 +1,408 @@
+#!/usr/bin/env python
+"""LUT-AMM benchmark: tokens/s through the LUT-NN approximate matrix multiply on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c1|c2|c3|c4|c5]
+                    [--impl ours|reference] [--shard m|n]
+
+One "step" is one pass of the hot path (closest-centroid search + LUT gather-accumulate +
+dequantise) over one batch of synthetic tokens for every linear of the workload.  Rank 0
+prints ONE JSON line.  Three measurements go into it:
+
+  value     device-resident: inputs and outputs already in HBM, calls queued on one stream,
+            timed with CUDA events on that stream, L2 flushed before every timed step
+  e2e       the same metric through the C ABI with pinned HOST buffers, so every step pays
+            its host->device and device->host copies inside the timed region
+  roofline  for the dominant kernel (the LUT gather/contraction kernel): its algorithmic
+            bytes per step divided by its device time, taken live with CUDA-event pairs
+            around each launch, against the measured HBM copy bandwidth
+
+and, at one GPU, `cpu_baseline`: the CPU oracle timed on this machine's host cores on a
+bounded sample.  `--impl reference` prints the CPU path's own line for the same workload.
+
+Multi-GPU (launched by torchrun, one rank per GPU): tokens are sharded across ranks and the
+weights replicated, so there is no data-path collective (weak scaling: every rank runs the
+full per-GPU batch).  `--shard n` instead shards the output columns and all-gathers the
+result with NCCL, for comparison.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+METRIC = "lut_amm_tokens_per_s"
+UNIT = "tokens/s"
+FALLBACK_HBM_GBS = 6650.0
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5"])
+    ap.add_argument("--variant", default="auto", choices=["auto", "gather", "umma", "tune"])
+    ap.add_argument("--shard", default="m", choices=["m", "n"])
+    ap.add_argument("--v", type=int, default=None, help="override sub-vector length (c5 sweep)")
+    ap.add_argument("--ct", type=int, default=None, help="override centroid count (c5 sweep)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["hbm_gbs"]), "measured"
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+def recorded_traffic(workload: str):
+    """DRAM bytes per step of the dominant kernel from the committed ncu capture, if any."""
+    p = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(p):
+        return json.load(open(p)).get(workload)
+    return None
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons while the timed region runs (read-only query)."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device: int):
+        self.device = device
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.device}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._pump, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for ln in self.proc.stdout:
+            self.lines.append(ln.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx = float(f[2])
+            except ValueError:
+                continue
+            for nm, val in zip(names, f[5:9]):
+                if val.lower() == "active":
+                    reasons.add(nm)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "samples": len(sm),
+                "reasons": sorted(reasons)}
+
+
+def workload_spec(args):
+    from pim_dl_asplos_b200 import synth
+    w = dict(synth.WORKLOADS[args.workload])
+    if args.v:
+        w["v"] = args.v
+    if args.ct:
+        w["CT"] = args.ct
+    return w
+
+
+# --------------------------------------------------------------------------- reference arm
+class CpuArm:
+    """The CPU oracle on `sample_tokens` tokens of the workload (weights built once)."""
+
+    def __init__(self, w, sample_tokens: int, threads: int):
+        import oracle
+        from pim_dl_asplos_b200 import synth
+        self.oracle, self.threads = oracle, threads
+        self.cases = []
+        for li, (_, K, N) in enumerate(w["linears"]):
+            cen, lut, bias = synth.make_weights(K, N, w["v"], w["CT"], seed=0, stream=li)
+            x = synth.make_input(sample_tokens, K, seed=0, stream=li)
+            self.cases.append((x, cen, lut, bias))
+
+    def step(self):
+        for x, cen, lut, bias in self.cases:
+            self.oracle.amm(x, cen, lut, bias, 0.01, 0.0, nthreads=self.threads)
+
+    def seconds_per_step(self, warmup: int, reps: int) -> float:
+        for _ in range(warmup):
+            self.step()
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            self.step()
+        return (time.perf_counter() - t0) / reps
+
+
+def pick_cpu_sample(w, budget_s: float, threads: int):
+    """Tokens per CPU step so that a step costs about `budget_s` seconds (bounded sample)."""
+    adds_per_token = sum((K // w["v"]) * N for _, K, N in w["linears"])
+    est_rate = 2.0e9 * threads  # byte-adds per second, conservative
+    tok = int(budget_s * est_rate / adds_per_token)
+    return max(16, min(w["M"], tok))
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import oracle
+    oracle.build()
+    w = workload_spec(args)
+    threads = os.cpu_count() or 1
+    # bounded sample: a step of about half a second of CPU work, so K steps end in minutes
+    tok = pick_cpu_sample(w, min(0.5, 60.0 / max(args.steps + args.warmup, 1)), threads)
+    sec = CpuArm(w, tok, threads).seconds_per_step(max(args.warmup, 1), max(args.steps, 1))
+    val = tok / sec
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": sec * 1e3 * (w["M"] / tok), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "fp32 search / int8->int32 gather", "data": "synthetic",
+        "config": config_dict(args, w),
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": "port",
+                         "sample": f"{tok} of {w['M']} tokens per step, {args.steps} steps; CPU restatement of the "
+                                   "reference AMM (search pinned bit-exact to the reference's index_calc_host.cpp), "
+                                   "gcc -O3 OpenMP, no -march"},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def config_dict(args, w):
+    return {"workload": f"{args.workload}: {w['what']}", "tokens_per_gpu": w["M"],
+            "linears": [{"name": n, "K": K, "N": N, "CB": K // w["v"]} for n, K, N in w["linears"]],
+            "sub_vec_len": w["v"], "num_centroid": w["CT"], "sharding": "tokens" if args.shard == "m" else "columns+allgather",
+            "l2_flush_between_steps": True, "variant": args.variant}
+
+
+# --------------------------------------------------------------------------- our arm
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    import pim_dl_asplos_b200 as P
+    from pim_dl_asplos_b200 import synth
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a GPU: the CUDA path has no CPU fallback")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    w = workload_spec(args)
+    M, v, CT = w["M"], w["v"], w["CT"]
+    if args.shard == "n" and world > 1:
+        from pim_dl_asplos_b200 import shard as sh
+    ctx = P.LutAmmContext(local)
+    stream = torch.cuda.Stream()
+    ctx.set_stream(stream.cuda_stream)
+
+    layers = []
+    for li, (name, K, N) in enumerate(w["linears"]):
+        cen, lut, bias = synth.make_weights(K, N, v, CT, seed=0, stream=li)
+        n_lo, n_hi = 0, N
+        if args.shard == "n" and world > 1:
+            n_lo, n_hi = sh.column_range(N, rank, world)
+            lut = np.ascontiguousarray(lut[:, :, n_lo:n_hi])
+            bias = np.ascontiguousarray(bias[n_lo:n_hi])
+        ctx.load_weights(li, cen, lut, bias, 0.01, 0.0)
+        x = synth.make_input(M, K, seed=rank, stream=li)
+        layers.append(dict(name=name, K=K, N=N, n_loc=n_hi - n_lo, x_host=x))
+        del cen, lut, bias
+    plan_variant = {"auto": P.VARIANT_AUTO, "gather": P.VARIANT_GATHER, "umma": P.VARIANT_UMMA}.get(args.variant)
+    for li, L in enumerate(layers):
+        if args.variant == "tune":
+            L["plan"] = ctx.tune(li, M)
+        else:
+            ctx.set_plan(li, variant=plan_variant)
+            L["plan"] = ctx.get_plan(li)
+
+    with torch.cuda.stream(stream):
+        for L in layers:
+            L["x_dev"] = torch.from_numpy(L["x_host"]).cuda(non_blocking=False)
+            L["y_dev"] = torch.empty(M, L["n_loc"], device="cuda", dtype=torch.float32)
+            if args.shard == "n" and world > 1:
+                L["y_all"] = torch.empty(world * M, L["n_loc"], device="cuda", dtype=torch.float32)
+                L["y_full"] = torch.empty(M, L["N"], device="cuda", dtype=torch.float32)
+        flush = torch.empty(256 * 1024 * 1024, device="cuda", dtype=torch.uint8)
+    stream.synchronize()
+
+    def step_device():
+        for li, L in enumerate(layers):
+            ctx.amm_host(li, L["x_dev"], L["y_dev"], n_tokens=M, flags=P.FLAG_ASYNC)
+            if args.shard == "n" and world > 1:
+                with torch.cuda.stream(stream):
+                    dist.all_gather_into_tensor(L["y_all"], L["y_dev"])
+                    # interleave the column slabs into row-major [M][N]
+                    L["y_full"].view(M, world, L["n_loc"]).copy_(L["y_all"].view(world, M, L["n_loc"]).permute(1, 0, 2))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(step_fn, steps, warmup):
+        for _ in range(warmup):
+            step_fn()
+        barrier()
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+        with torch.cuda.stream(stream):
+            for s, e in ev:
+                flush.zero_()          # evict L2 (256 MiB > 126 MB); outside the timed interval
+                s.record(stream)
+                step_fn()
+                e.record(stream)
+        barrier()
+        ms = sum(s.elapsed_time(e) for s, e in ev)
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches0 = ctx.launch_count
+    total_ms = timed(step_device, args.steps, max(args.warmup, 3))
+    gpu_launches = ctx.launch_count - launches0 - 0
+    # warm-up launches are inside that count; scale to the timed steps only
+    per_step_launches = (ctx.launch_count - launches0) // (args.steps + max(args.warmup, 3))
+    gpu_launches = per_step_launches * args.steps
+    ctx.sync()
+    ms_per_step = total_ms / args.steps
+    value = world * M / (ms_per_step * 1e-3)
+
+    # ---- roofline of the dominant kernel: CUDA-event pairs around each launch
+    ctx.enable_timing(True)
+    lut_ms = ccs_ms = 0.0
+    reps = min(args.steps, 20)
+    for _ in range(reps):
+        for li, L in enumerate(layers):
+            with torch.cuda.stream(stream):
+                flush.zero_()
+            ctx.amm_host(li, L["x_dev"], L["y_dev"], n_tokens=M)
+            t = ctx.timings()
+            lut_ms += t["lut_kernel_ms"]
+            ccs_ms += t["index_calc_ms"]
+    ctx.enable_timing(False)
+    lut_ms /= reps
+    ccs_ms /= reps
+    clocks = sampler.stop() if rank == 0 else None
+    alg = [synth.algorithmic_bytes(M, L["K"], L["n_loc"], v, CT) for L in layers]
+    lut_bytes = sum(a["lut"] for a in alg)
+    peak, peak_kind = peaks()
+    achieved = lut_bytes / (lut_ms * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "kernel": "lut gather-accumulate + dequantise (step 2+3), summed over the step's linears",
+                "achieved": achieved, "peak": peak, "peak_source": f"{peak_kind} HBM copy bandwidth",
+                "unit": "GB/s", "frac": achieved / peak, "traffic": recorded_traffic(args.workload),
+                "algorithmic_bytes_per_step": lut_bytes, "kernel_ms_per_step": lut_ms,
+                "search_kernel_ms_per_step": ccs_ms,
+                "search_algorithmic_bytes_per_step": sum(a["ccs"] for a in alg),
+                "whole_step_frac": (sum(a["total"] for a in alg) / (ms_per_step * 1e-3) / 1e9) / peak}
+
+    # ---- end to end: pinned host buffers through the public call, copies inside the timing
+    e2e = None
+    if not args.no_e2e:
+        for L in layers:
+            L["x_pin"] = torch.from_numpy(L["x_host"]).pin_memory()
+            L["y_pin"] = torch.empty(M, L["n_loc"], dtype=torch.float32).pin_memory()
+
+        def step_host():
+            for li, L in enumerate(layers):
+                ctx.amm_host(li, L["x_pin"], L["y_pin"], n_tokens=M)   # synchronous: H2D, kernels, D2H
+
+        for _ in range(3):
+            step_host()
+        barrier()
+        e_steps = max(3, min(args.steps, 30))
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record(stream)
+        t0 = time.perf_counter()
+        for _ in range(e_steps):
+            step_host()
+        e.record(stream)
+        barrier()
+        wall_ms = (time.perf_counter() - t0) * 1e3
+        dev_ms = s.elapsed_time(e)
+        tt = torch.tensor([max(wall_ms, dev_ms)], device="cuda", dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        e2e_ms = float(tt.item()) / e_steps
+        e2e = {"value": world * M / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
+               "h2d_bytes_per_step": sum(M * L["K"] * 4 for L in layers),
+               "d2h_bytes_per_step": sum(M * L["n_loc"] * 4 for L in layers), "steps": e_steps}
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        import oracle
+        oracle.build()
+        threads = os.cpu_count() or 1
+        tok = pick_cpu_sample(w, 2.0, threads)
+        sec = CpuArm(w, tok, threads).seconds_per_step(1, 5)
+        cpu = {"value": tok / sec, "unit": UNIT, "cores": threads, "kind": "port",
+               "sample": f"{tok} of {M} tokens per step, 1 warm-up + 5 timed steps, CPU restatement of the reference "
+                         "AMM (gcc -O3 OpenMP, no -march), search pinned bit-exact to the reference source"}
+
+    if rank == 0:
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "fp32 search / int8->int32 gather", "data": "synthetic",
+                "config": config_dict(args, w), "plans": [L["plan"] for L in layers],
+                "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": gpu_launches, "clocks": clocks}
+        print(json.dumps(line), flush=True)
+    ctx.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    world_env = int(os.environ.get("WORLD_SIZE", "0"))
+    if args.gpus > 1 and world_env == 0:
+        # convenience: relaunch under torchrun, one rank per GPU
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+               "--master-addr", "127.0.0.1", "--master-port", os.environ.get("MASTER_PORT", "29531"),
+               os.path.abspath(__file__)] + sys.argv[1:]
+        raise SystemExit(subprocess.call(cmd))
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()
