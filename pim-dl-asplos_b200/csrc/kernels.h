@@ -52,6 +52,7 @@ struct UmmaPlan {
     uint32_t n_tile;  // 64 / 128 / 256
     uint32_t split;   // CTAs sharing one output tile along the codebook axis
     uint32_t stages;
+    uint32_t max_ctas;  // persistent grid size cap: the SM count
 };
 bool umma_supported(uint32_t CB, uint32_t CT, uint32_t N);
 cudaError_t umma_make_tmap(CUtensorMap* out, const int8_t* lut_t, uint32_t CB, uint32_t CT, uint32_t N,
@@ -60,6 +61,7 @@ cudaError_t umma_make_tmap(CUtensorMap* out, const int8_t* lut_t, uint32_t CB, u
 cudaError_t launch_umma(const LutArgs& a, const CUtensorMap& lut_t_map, const UmmaPlan& p, int32_t* acc_scratch,
                         uint32_t* tile_counters, uint32_t* dev_err, cudaStream_t s, const char** why);
 void umma_default_plan(uint32_t M, uint32_t CB, uint32_t CT, uint32_t N, int sm_count, UmmaPlan* p);
+uint32_t umma_auto_split(uint32_t M, uint32_t CB, uint32_t CT, uint32_t N, uint32_t n_tile, int sm_count);
 
 // LUT [CB*CT][N] -> [N][CB*CT]
 cudaError_t launch_transpose_lut(const int8_t* lut, int8_t* lut_t, uint32_t rows, uint32_t cols, cudaStream_t s);

@@ -10,17 +10,24 @@
 // CT times faster.  The dequantisation (inference-engine/src/host/pim_lut_host.cpp:201)
 // is fused into the epilogue.
 //
-// Per CTA: one 128-token x N_TILE-column output tile, optionally only a slice of the
-// contraction axis (split > 1; partial sums meet in an int32 scratch tile in L2 with
-// coalesced red.add, and the CTA that arrives last dequantises and re-zeroes it).
+// Persistent kernel: one CTA per SM walks a list of work items, an item being one
+// 128-token x N_TILE-column output tile, or one slice of its contraction axis when
+// split > 1 (partial sums then meet in an int32 scratch tile in L2 through coalesced
+// red.add, and the CTA that arrives last dequantises the tile and re-zeroes the scratch).
+// The accumulator is double-buffered in TMEM so the epilogue of one item overlaps the
+// main loop of the next.
 //
-//   warp 0      TMA producer: B slabs = LUT^T[n0:n0+N_TILE][k:k+128] (K-major, 128-byte
-//               swizzle) from the load-time transposed copy of the LUT
-//   warp 1      owns TMEM (alloc/dealloc); one lane issues tcgen05.mma, 4 per 128-byte slab
-//   warps 2-5   build the one-hot A slab in shared memory straight from the uint8 indices
-//               (it never exists in HBM): for CT = 16 one codebook is exactly one 16-byte
-//               swizzle chunk, so a row is 8 vector stores; then run the epilogue, each
-//               warp reading its own 32-lane quadrant of the accumulator
+//   warp 0        TMA producer: B slabs = LUT^T[n0:n0+N_TILE][k:k+128] (K-major, 128-byte
+//                 swizzle) from the load-time transposed copy of the LUT
+//   warp 1        owns TMEM (alloc/dealloc); one lane issues tcgen05.mma, 4 per 128-byte slab
+//   warps 2-17    build the one-hot A slab in shared memory straight from the uint8 indices
+//                 (it never exists in HBM): four groups of four warps, group k taking every
+//                 fourth slab, one tile row per thread.  For CT = 16 one codebook is exactly
+//                 one 16-byte swizzle chunk, so a row is 8 vector stores.  Four groups because
+//                 a slab is a chain of latencies (index load, wait, proxy fence, arrive): they
+//                 have to overlap across slabs, not be shortened.
+//   warps 18-21   epilogue: TMEM -> registers -> shared-memory transpose -> dequantise ->
+//                 row-contiguous 16-byte global stores (each warp owns one 32-lane quadrant)
 //
 // HBM traffic: M*CB (indices) + CB*CT*N (LUT^T, once if L2-resident across M tiles)
 //              + 4*N (bias) + 4*M*N (output).
@@ -33,20 +40,25 @@ namespace lutamm {
 namespace {
 
 constexpr uint32_t kMTile = 128;
-constexpr uint32_t kSlabK = 128;              // bytes of K per pipeline stage = one swizzle row
+constexpr uint32_t kSlabK = 128;               // bytes of K per pipeline stage = one swizzle row
 constexpr uint32_t kABytes = kMTile * kSlabK;  // 16 KiB
-constexpr uint32_t kThreads = 192;
-constexpr uint32_t kEpiThreads = 128;
+constexpr uint32_t kAgenGroups = 4;  // each group: 4 warps = 128 rows
+constexpr uint32_t kAgenWarps = 4 * kAgenGroups, kEpiWarps = 4;
+constexpr uint32_t kEpiThreads = kEpiWarps * 32;
+constexpr uint32_t kFirstAgenWarp = 2, kFirstEpiWarp = kFirstAgenWarp + kAgenWarps;
+constexpr uint32_t kThreads = (kFirstEpiWarp + kEpiWarps) * 32;  // 704
 constexpr uint32_t kMaxStages = 8;
-constexpr uint32_t kStagingPitch = 33;        // words; conflict-free transposes
+constexpr uint32_t kStageWarpBytes = 32 * 128;           // epilogue transpose buffer per warp
 
 struct UmmaParams {
     LutArgs a;
-    uint32_t slabs_total;   // ceil(CB*CT / 128)
-    uint32_t slabs_per_cta; // ceil(slabs_total / split)
+    uint32_t slabs_total;    // ceil(CB*CT / 128)
+    uint32_t slabs_per_item; // ceil(slabs_total / split)
     uint32_t split;
     uint32_t stages;
-    int32_t* acc_scratch;   // [M][N] int32, all zero between launches (split > 1)
+    uint32_t tiles_m, tiles_n;
+    uint32_t log2_ct;
+    int32_t* acc_scratch;    // [M][N] int32, all zero between launches (split > 1)
     uint32_t* tile_counters;
     uint32_t* dev_err;
 };
@@ -54,7 +66,6 @@ struct UmmaParams {
 __device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t n) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n) : "memory");
 }
-
 // 16 bytes with byte `i` (0..15) set to 1; i >= 16 gives zeros.
 __device__ __forceinline__ uint4 onehot16(uint32_t i) {
     const uint32_t bit = 1u << ((i & 3u) * 8u);
@@ -62,43 +73,55 @@ __device__ __forceinline__ uint4 onehot16(uint32_t i) {
     return make_uint4(q == 0 ? bit : 0u, q == 1 ? bit : 0u, q == 2 ? bit : 0u, q == 3 ? bit : 0u);
 }
 
+struct Item {
+    uint32_t m0, n0, slab_begin, nslab, tile;
+};
+__device__ __forceinline__ Item decode_item(const UmmaParams& p, uint32_t item, uint32_t n_tile) {
+    Item it;
+    const uint32_t z = item % p.split, tile = item / p.split;
+    it.tile = tile;
+    it.m0 = (tile % p.tiles_m) * kMTile;
+    it.n0 = (tile / p.tiles_m) * n_tile;
+    it.slab_begin = z * p.slabs_per_item;
+    const uint32_t end = min(p.slabs_total, it.slab_begin + p.slabs_per_item);
+    it.nslab = end > it.slab_begin ? end - it.slab_begin : 0u;
+    return it;
+}
+
 template <uint32_t N_TILE>
 __global__ void __launch_bounds__(kThreads, 1)
 lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const UmmaParams p) {
     constexpr uint32_t kBBytes = N_TILE * kSlabK;
     constexpr uint32_t kIdesc = umma_idesc_i8(kMTile, N_TILE, /*a_signed=*/1, /*b_signed=*/1);
-    constexpr uint32_t kTmemCols = N_TILE < 32 ? 32 : N_TILE;
+    constexpr uint32_t kTmemCols = 2 * N_TILE < 32 ? 32 : 2 * N_TILE;  // two accumulators
 
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     const uint32_t S = p.stages;
-    unsigned char* s_a = smem;                                  // [S][16 KiB], 1024-aligned
-    unsigned char* s_b = s_a + (size_t)S * kABytes;             // [S][N_TILE*128], 1024-aligned
-    float* s_bias = reinterpret_cast<float*>(s_b + (size_t)S * kBBytes);              // [N_TILE]
-    uint32_t* s_stage = reinterpret_cast<uint32_t*>(s_bias + N_TILE);                 // [4][32][33]
-    uint64_t* s_bar = reinterpret_cast<uint64_t*>(s_stage + 4 * 32 * kStagingPitch);  // 3*S + 1
-    uint32_t* s_misc = reinterpret_cast<uint32_t*>(s_bar + 3 * kMaxStages + 1);       // tmem base, abort, last
+    unsigned char* s_a = smem;                                   // [S][16 KiB], 1024-aligned
+    unsigned char* s_b = s_a + (size_t)S * kABytes;              // [S][N_TILE*128], 1024-aligned
+    unsigned char* s_stage = s_b + (size_t)S * kBBytes;          // [4][32][128] epilogue transpose
+    uint64_t* s_bar = reinterpret_cast<uint64_t*>(s_stage + kEpiWarps * kStageWarpBytes);
+    uint32_t* s_misc = reinterpret_cast<uint32_t*>(s_bar + 2 * kMaxStages + 4);  // tmem base, abort, last
     volatile uint32_t* s_abort = s_misc + 1;
 
-    const uint32_t full_a0 = smem_u32(s_bar), full_b0 = smem_u32(s_bar + kMaxStages),
-                   empty0 = smem_u32(s_bar + 2 * kMaxStages), acc_full = smem_u32(s_bar + 3 * kMaxStages);
+    const uint32_t full0 = smem_u32(s_bar), empty0 = smem_u32(s_bar + kMaxStages),
+                   acc_full0 = smem_u32(s_bar + 2 * kMaxStages), acc_empty0 = smem_u32(s_bar + 2 * kMaxStages + 2);
 
     const LutArgs& a = p.a;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t n0 = blockIdx.x * N_TILE, m0 = blockIdx.y * kMTile;
-    const uint32_t slab_begin = blockIdx.z * p.slabs_per_cta;
-    const uint32_t slab_end = min(p.slabs_total, slab_begin + p.slabs_per_cta);
-    const uint32_t nslab = slab_end > slab_begin ? slab_end - slab_begin : 0u;
-    const uint32_t Kg = a.CB * a.CT;
+    const uint32_t n_items = p.tiles_m * p.tiles_n * p.split;
 
     if (threadIdx.x == 0) {
         s_misc[0] = 0; s_misc[1] = 0; s_misc[2] = 0;
         for (uint32_t s = 0; s < S; ++s) {
-            mbar_init(full_a0 + 8 * s, kEpiThreads);
-            mbar_init(full_b0 + 8 * s, 1);
-            mbar_init(empty0 + 8 * s, 1);
+            mbar_init(full0 + 8 * s, 4 + 1);           // the four warps of one A-builder group + the TMA
+            mbar_init(empty0 + 8 * s, 1);              // tcgen05.commit
         }
-        mbar_init(acc_full, 1);
+        for (uint32_t b = 0; b < 2; ++b) {
+            mbar_init(acc_full0 + 8 * b, 1);           // tcgen05.commit
+            mbar_init(acc_empty0 + 8 * b, kEpiWarps);
+        }
         fence_barrier_init();
         tma_prefetch_desc(&lut_t_map);
     }
@@ -112,205 +135,249 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
     tc_fence_after_sync();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(s_misc);
 
-    uint32_t b_issued = 0;
     if (warp == 0) {
         // ---------------- TMA producer (the LUT never depends on the preceding kernel)
         if (lane == 0) {
-            for (uint32_t i = 0; i < nslab; ++i) {
-                const uint32_t s = i % S, ph = (i / S) & 1;
-                if (!mbar_wait(empty0 + 8 * s, ph ^ 1, s_abort)) break;
-                mbar_arrive_expect_tx(full_b0 + 8 * s, kBBytes);
-                tma_load_2d(smem_u32(s_b + (size_t)s * kBBytes), &lut_t_map, full_b0 + 8 * s,
-                            (int32_t)((slab_begin + i) * kSlabK), (int32_t)n0);
-                b_issued = i + 1;
+            uint32_t g = 0;
+            bool ok = true;
+            for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+                const Item it = decode_item(p, item, N_TILE);
+                for (uint32_t i = 0; i < it.nslab; ++i, ++g) {
+                    const uint32_t s = g % S, ph = (g / S) & 1;
+                    ok = mbar_wait(empty0 + 8 * s, ph ^ 1, s_abort);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(full0 + 8 * s, kBBytes);
+                    tma_load_2d(smem_u32(s_b + (size_t)s * kBBytes), &lut_t_map, full0 + 8 * s,
+                                (int32_t)((it.slab_begin + i) * kSlabK), (int32_t)it.n0);
+                }
             }
         }
         __syncwarp();
     } else if (warp == 1) {
         // ---------------- MMA issuer
         if (lane == 0) {
+            uint32_t g = 0, t = 0;
             bool ok = true;
-            for (uint32_t i = 0; i < nslab && ok; ++i) {
-                const uint32_t s = i % S, ph = (i / S) & 1;
-                ok = mbar_wait(full_a0 + 8 * s, ph, s_abort) && mbar_wait(full_b0 + 8 * s, ph, s_abort);
+            for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++t) {
+                const Item it = decode_item(p, item, N_TILE);
+                const uint32_t ab = t & 1, aph = (t >> 1) & 1;
+                ok = mbar_wait(acc_empty0 + 8 * ab, aph ^ 1, s_abort);  // epilogue drained this buffer
                 if (!ok) break;
                 tc_fence_after_sync();
-                const uint64_t da = umma_desc_k_sw128(smem_u32(s_a + (size_t)s * kABytes));
-                const uint64_t db = umma_desc_k_sw128(smem_u32(s_b + (size_t)s * kBBytes));
+                const uint32_t d_tmem = tmem_base + ab * N_TILE;
+                for (uint32_t i = 0; i < it.nslab; ++i, ++g) {
+                    const uint32_t s = g % S, ph = (g / S) & 1;
+                    ok = mbar_wait(full0 + 8 * s, ph, s_abort);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    const uint64_t da = umma_desc_k_sw128(smem_u32(s_a + (size_t)s * kABytes));
+                    const uint64_t db = umma_desc_k_sw128(smem_u32(s_b + (size_t)s * kBBytes));
 #pragma unroll
-                for (uint32_t kk = 0; kk < kSlabK / 32; ++kk)  // 32 bytes of K per instruction
-                    umma_i8(tmem_base, da + 2 * kk, db + 2 * kk, kIdesc, (i | kk) != 0 ? 1u : 0u);
-                umma_commit(empty0 + 8 * s);  // frees the stage once these MMAs have read it
+                    for (uint32_t kk = 0; kk < kSlabK / 32; ++kk)  // 32 bytes of K per instruction
+                        umma_i8(d_tmem, da + 2 * kk, db + 2 * kk, kIdesc, (i | kk) != 0 ? 1u : 0u);
+                    umma_commit(empty0 + 8 * s);  // frees the stage once these MMAs have read it
+                }
+                if (ok) umma_commit(acc_full0 + 8 * ab);
             }
-            if (ok && nslab) umma_commit(acc_full);
         }
         __syncwarp();
+    } else if (warp < kFirstEpiWarp) {
+        // ---------------- one-hot A builders: kAgenGroups groups of 4 warps; group k owns
+        // every kAgenGroups-th slab of the CTA's slab sequence, one tile row per thread, so
+        // the fixed latencies of a slab (index load, wait, proxy fence, arrive) overlap
+        // across groups instead of adding up.
+        // The indices come from the kernel launched just before; ld.global.cg reads them from
+        // L2, which matters because under programmatic dependent launch this CTA may have
+        // started, on an SM with older lines in L1, before that kernel finished.
+        pdl_wait_prior_grid();
+        const uint32_t grp = (warp - kFirstAgenWarp) >> 2;
+        const uint32_t r = (warp & 3u) * 32 + lane;  // tile row
+        const uint32_t sw = r & 7u;
+        const uint32_t CT = a.CT, lg = p.log2_ct;
+        // bytes of index one slab needs per row: 128 / CT codebooks (at least one byte)
+        auto load_raw = [&](const uint8_t* row, uint32_t slab) -> uint4 {
+            const uint8_t* q = row + ((slab * kSlabK) >> lg);
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (lg == 4) { const uint2 t = __ldcg(reinterpret_cast<const uint2*>(q)); v.x = t.x; v.y = t.y; }
+            else if (lg == 3) v = __ldcg(reinterpret_cast<const uint4*>(q));
+            else if (lg == 5) v.x = __ldcg(reinterpret_cast<const uint32_t*>(q));
+            else if (lg == 6) v.x = __ldcg(reinterpret_cast<const uint16_t*>(q));
+            else v.x = __ldcg(q);
+            return v;
+        };
+        uint32_t g = 0;
+        bool ok = true;
+        for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+            const Item it = decode_item(p, item, N_TILE);
+            const uint8_t* grow = a.idx + (size_t)min(it.m0 + r, a.M - 1) * a.CB;  // rows past M: masked in the epilogue
+            uint32_t i = (grp + kAgenGroups - (g % kAgenGroups)) % kAgenGroups;
+            uint4 raw_next = make_uint4(0, 0, 0, 0);
+            if (i < it.nslab) raw_next = load_raw(grow, it.slab_begin + i);
+            for (; i < it.nslab && ok; i += kAgenGroups) {
+                const uint32_t slab = it.slab_begin + i;
+                const uint4 raw = raw_next;
+                if (i + kAgenGroups < it.nslab) raw_next = load_raw(grow, slab + kAgenGroups);
+                uint4 chunk[8];
+                if (lg == 4) {  // one codebook == one 16-byte chunk
+#pragma unroll
+                    for (uint32_t j = 0; j < 8; ++j)
+                        chunk[j] = onehot16(((j < 4 ? raw.x : raw.y) >> (8 * (j & 3))) & 0xFFu);
+                } else if (lg == 3) {  // two codebooks per chunk
+                    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                    for (uint32_t j = 0; j < 8; ++j) {
+                        const uint32_t two = (w[j >> 1] >> (16 * (j & 1))) & 0xFFFFu;
+                        const uint4 lo = onehot16(two & 7u), hi = onehot16(((two >> 8) & 7u) + 8u);
+                        chunk[j] = make_uint4(lo.x | hi.x, lo.y | hi.y, lo.z | hi.z, lo.w | hi.w);
+                    }
+                } else {  // a codebook spans CT/16 chunks
+#pragma unroll
+                    for (uint32_t j = 0; j < 8; ++j) {
+                        const uint32_t k0 = slab * kSlabK + 16 * j;
+                        const uint32_t ix = (raw.x >> (8 * (j >> (lg - 4)))) & 0xFFu;  // CT >= 128: always byte 0
+                        const uint32_t sub = (k0 & (CT - 1)) >> 4;
+                        chunk[j] = onehot16((ix >> 4) == sub ? (ix & 15u) : 16u);
+                    }
+                }
+                const uint32_t gg = g + i, s = gg % S, ph = (gg / S) & 1;
+                uint32_t w_ok = 1;
+                if (lane == 0) w_ok = mbar_wait(empty0 + 8 * s, ph ^ 1, s_abort) ? 1u : 0u;
+                ok = __shfl_sync(0xffffffffu, w_ok, 0) != 0;
+                if (!ok) break;
+                unsigned char* row_ptr = s_a + (size_t)s * kABytes + r * kSlabK;
+#pragma unroll
+                for (uint32_t j = 0; j < 8; ++j)  // 128-byte swizzle: 16-byte chunk j of row r lands at j ^ (r & 7)
+                    *reinterpret_cast<uint4*>(row_ptr + ((j ^ sw) << 4)) = chunk[j];
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(full0 + 8 * s);
+            }
+            g += it.nslab;
+        }
     } else {
-        // ---------------- one-hot A builder, then epilogue (warps 2..5 -> TMEM quadrants 2,3,0,1)
-        // The indices come from the kernel launched just before; they are read with ld.cg
-        // (L2) because under programmatic dependent launch this CTA may have started, on an
-        // SM with older lines in L1, before that kernel finished.
+        // ---------------- epilogue (warps 18..21 -> TMEM lane quadrants 2,3,0,1)
         pdl_wait_prior_grid();
         const uint32_t quad = warp & 3u;
-        const uint32_t r = quad * 32 + lane;       // row of the tile == TMEM lane
-        const uint32_t m = m0 + r;
-        const bool row_ok = m < a.M;
-        const uint8_t* idx_row = a.idx + (size_t)(row_ok ? m : 0) * a.CB;
-        const uint32_t et = threadIdx.x - 64;      // 0..127
-        for (uint32_t i = et; i < N_TILE; i += kEpiThreads) s_bias[i] = (n0 + i < a.N) ? __ldg(a.bias + n0 + i) : 0.f;
-
-        const uint32_t sw = r & 7u;
-        const bool fast16 = (a.CT == 16) && (a.CB % 8 == 0) && ((reinterpret_cast<uintptr_t>(a.idx) & 7u) == 0);
+        const uint32_t et = threadIdx.x - kFirstEpiWarp * 32;
+        const float lbcb = lut_bias_times_cb(a.lut_bias, a.CB);
+        unsigned char* stg = s_stage + (warp - kFirstEpiWarp) * kStageWarpBytes;
+        const uint32_t rsw = lane & 7u;
+        const uint32_t ch = lane & 7u, rsub = lane >> 3;  // store phase: 16-byte column group, row within a pass
+        uint32_t t = 0;
         bool ok = true;
-        for (uint32_t i = 0; i < nslab && ok; ++i) {
-            const uint32_t s = i % S, ph = (i / S) & 1;
-            const uint32_t kbase = (slab_begin + i) * kSlabK;
-            uint4 chunk[8];
-            if (fast16) {
-                // one codebook == one 16-byte chunk; 8 codebooks per slab
-                uint2 raw = make_uint2(0xFFFFFFFFu, 0xFFFFFFFFu);
-                if (row_ok) raw = __ldcg(reinterpret_cast<const uint2*>(idx_row + (kbase >> 4)));
-#pragma unroll
-                for (uint32_t j = 0; j < 8; ++j) {
-                    const uint32_t word = j < 4 ? raw.x : raw.y;
-                    const uint32_t ix = (word >> (8 * (j & 3))) & 0xFFu;
-                    chunk[j] = onehot16(row_ok ? ix : 16u);
-                }
-            } else {
-#pragma unroll
-                for (uint32_t j = 0; j < 8; ++j) {
-                    const uint32_t k0 = kbase + j * 16;
-                    uint4 c = make_uint4(0, 0, 0, 0);
-                    if (row_ok && k0 < Kg) {
-                        if (a.CT >= 16) {
-                            const uint32_t cb = k0 / a.CT, sub = (k0 % a.CT) >> 4;
-                            const uint32_t ix = __ldcg(idx_row + cb);
-                            if ((ix >> 4) == sub) c = onehot16(ix & 15u);
-                        } else {  // CT == 8: two codebooks share the chunk
-                            const uint32_t cb = k0 >> 3;
-                            const uint32_t i0 = __ldcg(idx_row + cb);
-                            const uint32_t i1 = (cb + 1 < a.CB) ? __ldcg(idx_row + cb + 1) : 8u;
-                            const uint4 lo = onehot16(i0 & 7u), hi = onehot16(i1 < 8u ? i1 + 8u : 16u);
-                            c = make_uint4(lo.x | hi.x, lo.y | hi.y, lo.z | hi.z, lo.w | hi.w);
-                        }
+        for (uint32_t item = blockIdx.x; item < n_items; item += gridDim.x, ++t) {
+            const Item it = decode_item(p, item, N_TILE);
+            const uint32_t ab = t & 1, aph = (t >> 1) & 1;
+            uint32_t w_ok = 1;
+            if (lane == 0) w_ok = (ok && mbar_wait(acc_full0 + 8 * ab, aph, s_abort)) ? 1u : 0u;
+            ok = __shfl_sync(0xffffffffu, w_ok, 0) != 0;
+            if (ok) {
+                tc_fence_after_sync();
+                for (uint32_t c = 0; c < N_TILE / 32; ++c) {
+                    uint32_t v[32];
+                    tmem_ld_32x32b_x32(tmem_base + ((quad * 32u) << 16) + ab * N_TILE + c * 32u, v);
+                    tmem_ld_wait();
+                    if (c == N_TILE / 32 - 1) {  // accumulator fully read: hand the buffer back
+                        tc_fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(acc_empty0 + 8 * ab);
                     }
-                    chunk[j] = c;
-                }
-            }
-            ok = mbar_wait(empty0 + 8 * s, ph ^ 1, s_abort);
-            if (!ok) break;
-            unsigned char* row_ptr = s_a + (size_t)s * kABytes + r * kSlabK;
-#pragma unroll
-            for (uint32_t j = 0; j < 8; ++j)  // 128-byte swizzle: 16-byte chunk j of row r lands at j ^ (r & 7)
-                *reinterpret_cast<uint4*>(row_ptr + ((j ^ sw) << 4)) = chunk[j];
-            fence_proxy_async_smem();
-            mbar_arrive(full_a0 + 8 * s);
-        }
-
-        // ---------------- epilogue
-        if (ok && nslab) ok = mbar_wait(acc_full, 0, s_abort);
-        // Bias tile visible; every epilogue thread is past its waits, so the abort word is
-        // final from here on and the branch below is uniform across the 128 threads (it
-        // contains further named barriers).
-        named_bar_sync(1, kEpiThreads);
-        if (nslab && !*s_abort) {
-            tc_fence_after_sync();
-            const float lbcb = lut_bias_times_cb(a.lut_bias, a.CB);
-            uint32_t* stg = s_stage + quad * 32 * kStagingPitch;
-            for (uint32_t c = 0; c < N_TILE / 32; ++c) {
-                uint32_t v[32];
-                tmem_ld_32x32b_x32(tmem_base + ((quad * 32u) << 16) + c * 32u, v);
-                tmem_ld_wait();
-                const uint32_t nc = n0 + c * 32;
-                if (p.split == 1 && !a.layout.tiled) {
-                    if (row_ok && nc < a.N) {
-                        // N % 16 == 0 and nc % 32 == 0: the 32 columns are in range in groups of 16
-                        const uint32_t lim = min(32u, a.N - nc);
-                        float4* dst = reinterpret_cast<float4*>(a.out + (size_t)m * a.N + nc);
-                        int4* adst = a.acc_out ? reinterpret_cast<int4*>(a.acc_out + (size_t)m * a.N + nc) : nullptr;
-#pragma unroll
-                        for (uint32_t q = 0; q < 8; ++q) {
-                            if (4 * q < lim) {
-                                const float4 b = *reinterpret_cast<const float4*>(s_bias + c * 32 + 4 * q);
-                                float4 o;
-                                o.x = dequant_one((int32_t)v[4 * q + 0], a.scale, lbcb, b.x);
-                                o.y = dequant_one((int32_t)v[4 * q + 1], a.scale, lbcb, b.y);
-                                o.z = dequant_one((int32_t)v[4 * q + 2], a.scale, lbcb, b.z);
-                                o.w = dequant_one((int32_t)v[4 * q + 3], a.scale, lbcb, b.w);
-                                dst[q] = o;
-                                if (adst) adst[q] = make_int4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-                            }
-                        }
-                    }
-                } else {
-                    // transpose through shared memory so that a warp touches 32 consecutive
-                    // columns of one row per instruction (coalesced stores / reductions)
                     __syncwarp();
 #pragma unroll
-                    for (uint32_t j = 0; j < 32; ++j) stg[lane * kStagingPitch + j] = v[j];
+                    for (uint32_t q = 0; q < 8; ++q)
+                        *reinterpret_cast<uint4*>(stg + lane * 128 + ((q ^ rsw) << 4)) =
+                            make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
                     __syncwarp();
-                    const uint32_t n = nc + lane;
-                    for (uint32_t rr = 0; rr < 32; ++rr) {
-                        const uint32_t mm = m0 + quad * 32 + rr;
-                        if (mm >= a.M) break;
-                        if (n < a.N) {
-                            const int32_t val = (int32_t)stg[rr * kStagingPitch + lane];
+                    const uint32_t n = it.n0 + c * 32 + ch * 4;
+                    if (n < a.N) {  // N % 16 == 0: a 4-column group is in or out as a whole
+                        const float4 b4 = __ldg(reinterpret_cast<const float4*>(a.bias + n));
+#pragma unroll
+                        for (uint32_t pass = 0; pass < 8; ++pass) {
+                            const uint32_t rr = pass * 4 + rsub;
+                            const uint32_t mm = it.m0 + quad * 32 + rr;
+                            if (mm >= a.M) continue;
+                            const int4 val = *reinterpret_cast<const int4*>(stg + rr * 128 + ((ch ^ (rr & 7u)) << 4));
                             if (p.split == 1) {
-                                const float o = dequant_one(val, a.scale, lbcb, s_bias[c * 32 + lane]);
-                                a.out[tiled_out_offset(mm, n, a.layout)] = o;
-                                if (a.acc_out) a.acc_out[(size_t)mm * a.N + n] = val;
+                                float4 o;
+                                o.x = dequant_one(val.x, a.scale, lbcb, b4.x);
+                                o.y = dequant_one(val.y, a.scale, lbcb, b4.y);
+                                o.z = dequant_one(val.z, a.scale, lbcb, b4.z);
+                                o.w = dequant_one(val.w, a.scale, lbcb, b4.w);
+                                if (!a.layout.tiled) {
+                                    *reinterpret_cast<float4*>(a.out + (size_t)mm * a.N + n) = o;
+                                } else {
+                                    a.out[tiled_out_offset(mm, n + 0, a.layout)] = o.x;
+                                    a.out[tiled_out_offset(mm, n + 1, a.layout)] = o.y;
+                                    a.out[tiled_out_offset(mm, n + 2, a.layout)] = o.z;
+                                    a.out[tiled_out_offset(mm, n + 3, a.layout)] = o.w;
+                                }
+                                if (a.acc_out) *reinterpret_cast<int4*>(a.acc_out + (size_t)mm * a.N + n) = val;
                             } else {
-                                atomicAdd(p.acc_scratch + (size_t)mm * a.N + n, val);
+                                int32_t* dst = p.acc_scratch + (size_t)mm * a.N + n;
+                                atomicAdd(dst + 0, val.x);
+                                atomicAdd(dst + 1, val.y);
+                                atomicAdd(dst + 2, val.z);
+                                atomicAdd(dst + 3, val.w);
                             }
                         }
                     }
                 }
             }
             if (p.split > 1) {
-                // last CTA of this output tile dequantises the summed tile and re-zeroes it
+                // The CTA that arrives last at this output tile dequantises the summed tile and
+                // re-zeroes the scratch.  Every epilogue thread runs the barriers, also after a
+                // failed wait, so nobody is left behind at one.
                 __threadfence();
                 named_bar_sync(1, kEpiThreads);
                 if (et == 0) {
-                    uint32_t* ctr = p.tile_counters + blockIdx.y * gridDim.x + blockIdx.x;
-                    const uint32_t old = atomicAdd(ctr, 1u);
-                    const uint32_t last = (old == p.split - 1) ? 1u : 0u;
-                    if (last) *ctr = 0u;
+                    uint32_t last = 0;
+                    if (ok && !*s_abort) {
+                        uint32_t* ctr = p.tile_counters + it.tile;
+                        const uint32_t old = atomicAdd(ctr, 1u);
+                        last = (old == p.split - 1) ? 1u : 0u;
+                        if (last) *ctr = 0u;
+                    }
                     s_misc[2] = last;
                 }
                 named_bar_sync(1, kEpiThreads);
                 if (s_misc[2]) {
                     __threadfence();
-                    for (uint32_t rr = 0; rr < 32; ++rr) {
-                        const uint32_t mm = m0 + quad * 32 + rr;
-                        if (mm >= a.M) break;
+                    for (uint32_t pass = 0; pass < 8; ++pass) {
+                        const uint32_t mm = it.m0 + quad * 32 + pass * 4 + rsub;
+                        if (mm >= a.M) continue;
                         for (uint32_t c = 0; c < N_TILE / 32; ++c) {
-                            const uint32_t n = n0 + c * 32 + lane;
-                            if (n < a.N) {
-                                int32_t* src = p.acc_scratch + (size_t)mm * a.N + n;
-                                const int32_t val = __ldcg(src);
-                                __stcg(src, 0);
-                                const float o = dequant_one(val, a.scale, lbcb, s_bias[c * 32 + lane]);
-                                if (a.layout.tiled) a.out[tiled_out_offset(mm, n, a.layout)] = o;
-                                else a.out[(size_t)mm * a.N + n] = o;
-                                if (a.acc_out) a.acc_out[(size_t)mm * a.N + n] = val;
+                            const uint32_t n = it.n0 + c * 32 + ch * 4;
+                            if (n >= a.N) continue;
+                            int4* src = reinterpret_cast<int4*>(p.acc_scratch + (size_t)mm * a.N + n);
+                            const int4 val = __ldcg(src);
+                            __stcg(src, make_int4(0, 0, 0, 0));
+                            const float4 b4 = __ldg(reinterpret_cast<const float4*>(a.bias + n));
+                            float o[4] = {dequant_one(val.x, a.scale, lbcb, b4.x), dequant_one(val.y, a.scale, lbcb, b4.y),
+                                          dequant_one(val.z, a.scale, lbcb, b4.z), dequant_one(val.w, a.scale, lbcb, b4.w)};
+                            if (!a.layout.tiled) {
+                                *reinterpret_cast<float4*>(a.out + (size_t)mm * a.N + n) = make_float4(o[0], o[1], o[2], o[3]);
+                            } else {
+#pragma unroll
+                                for (uint32_t k = 0; k < 4; ++k) a.out[tiled_out_offset(mm, n + k, a.layout)] = o[k];
                             }
+                            if (a.acc_out) *reinterpret_cast<int4*>(a.acc_out + (size_t)mm * a.N + n) = val;
                         }
                     }
                 }
+                named_bar_sync(1, kEpiThreads);  // s_misc[2] is rewritten by the next item
             }
-            tc_fence_before_sync();
         }
+        tc_fence_before_sync();
     }
 
     // ---------------- tear-down (also the way out after a wait that ran out)
     __syncthreads();
     if (*s_abort) {
         if (threadIdx.x == 0) {
-            // let B copies still in flight land before the shared memory is given back
-            const uint32_t first = b_issued > S ? b_issued - S : 0u;
-            for (uint32_t i = first; i < b_issued; ++i)
-                for (uint32_t it = 0; it < kWaitLimit; ++it)
-                    if (mbar_try_wait(full_b0 + 8 * (i % S), (i / S) & 1)) break;
+            // Give B copies that may still be in flight time to land before the shared memory is
+            // handed back: a TMA tile arrives within microseconds; wait a bounded ~100 us.
+            const long long t0 = clock64();
+            while (clock64() - t0 < 200000) {}
             atomicExch(p.dev_err, 2u);
         }
         __syncthreads();
@@ -322,17 +389,18 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
 }
 
 size_t umma_smem_bytes(uint32_t n_tile, uint32_t stages) {
-    return (size_t)stages * (kABytes + n_tile * kSlabK) + n_tile * 4 + 4 * 32 * kStagingPitch * 4 +
-           (3 * kMaxStages + 1) * 8 + 16 + 1024;
+    return (size_t)stages * (kABytes + n_tile * kSlabK) + kEpiWarps * kStageWarpBytes +
+           (2 * kMaxStages + 4) * 8 + 16 + 1024;
 }
+constexpr size_t kSmemLimit = 227 * 1024;
 
 template <uint32_t N_TILE>
-cudaError_t run(const CUtensorMap& map, const UmmaParams& p, dim3 grid, size_t smem, cudaStream_t s) {
+cudaError_t run(const CUtensorMap& map, const UmmaParams& p, uint32_t grid, size_t smem, cudaStream_t s) {
     auto k = lut_onehot_umma_kernel<N_TILE>;
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid;
+    cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(kThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = s;
@@ -344,39 +412,46 @@ cudaError_t run(const CUtensorMap& map, const UmmaParams& p, dim3 grid, size_t s
     return cudaLaunchKernelEx(&cfg, k, map, p);
 }
 
+uint32_t default_stages(uint32_t n_tile) {
+    uint32_t st = kMaxStages;
+    while (st > 2 && umma_smem_bytes(n_tile, st) > kSmemLimit) --st;
+    return st;
+}
+
 }  // namespace
 
 bool umma_supported(uint32_t CB, uint32_t CT, uint32_t N) {
     const bool ct_ok = CT == 8 || CT == 16 || CT == 32 || CT == 64 || CT == 128 || CT == 256;
-    return ct_ok && ((uint64_t)CB * CT) % 16 == 0 && N % 16 == 0 && CB > 0 && N > 0;
+    // CB % 16: the index tile is staged in 16-byte pieces; it also makes CB*CT a multiple of 128
+    return ct_ok && CB > 0 && CB % 16 == 0 && N > 0 && N % 16 == 0;
 }
 
-void umma_default_plan(uint32_t M, uint32_t CB, uint32_t CT, uint32_t N, int sm_count, UmmaPlan* p) {
-    uint32_t n_tile = N >= 256 ? 256 : (N > 64 ? 128 : 64);
+uint32_t umma_auto_split(uint32_t M, uint32_t CB, uint32_t CT, uint32_t N, uint32_t n_tile, int sm_count) {
     const uint32_t slabs = (uint32_t)(((uint64_t)CB * CT + kSlabK - 1) / kSlabK);
-    uint32_t tiles = ((M + kMTile - 1) / kMTile) * ((N + n_tile - 1) / n_tile);
-    if (n_tile == 256 && tiles < (uint32_t)sm_count / 2 && N >= 512) {
-        // few tiles: narrower tiles first, then split the contraction axis
-        n_tile = 128;
-        tiles = ((M + kMTile - 1) / kMTile) * ((N + n_tile - 1) / n_tile);
-    }
+    const uint32_t tiles = ((M + kMTile - 1) / kMTile) * ((N + n_tile - 1) / n_tile);
     uint32_t split = 1;
     if (tiles < (uint32_t)sm_count) {
         split = (uint32_t)sm_count / tiles;
-        const uint32_t max_split = slabs / 8 ? slabs / 8 : 1;  // keep at least 8 slabs per CTA
+        const uint32_t max_split = slabs / 8 ? slabs / 8 : 1;  // keep at least 8 slabs per item
         if (split > max_split) split = max_split;
         if (split > 16) split = 16;
         if (split < 1) split = 1;
     }
+    return split;
+}
+
+void umma_default_plan(uint32_t M, uint32_t CB, uint32_t CT, uint32_t N, int sm_count, UmmaPlan* p) {
+    uint32_t n_tile = N >= 256 ? 256 : (N > 64 ? 128 : 64);
     p->n_tile = n_tile;
-    p->split = split;
-    p->stages = n_tile == 256 ? 4 : (n_tile == 128 ? 6 : 8);
+    p->split = umma_auto_split(M, CB, CT, N, n_tile, sm_count);
+    p->stages = default_stages(n_tile);
+    p->max_ctas = (uint32_t)sm_count;
 }
 
 cudaError_t umma_make_tmap(CUtensorMap* out, const int8_t* lut_t, uint32_t CB, uint32_t CT, uint32_t N,
                            uint32_t n_tile, const char** why) {
     *why = nullptr;
-    if (!umma_supported(CB, CT, N)) { *why = "tcgen05 variant: needs num_centroid in {8,16,32,64,128,256}, CB*CT % 16 == 0, N % 16 == 0"; return cudaErrorInvalidValue; }
+    if (!umma_supported(CB, CT, N)) { *why = "tcgen05 variant: needs num_centroid in {8,16,32,64,128,256}, num_codebook % 16 == 0, N % 16 == 0"; return cudaErrorInvalidValue; }
     if (n_tile != 64 && n_tile != 128 && n_tile != 256) { *why = "tcgen05 variant: N tile must be 64, 128 or 256"; return cudaErrorInvalidValue; }
     EncodeTiledFn enc = get_encode_tiled();
     if (!enc) { *why = "cuTensorMapEncodeTiled is not available from this driver"; return cudaErrorNotSupported; }
@@ -396,24 +471,31 @@ cudaError_t launch_umma(const LutArgs& a, const CUtensorMap& lut_t_map, const Um
                         uint32_t* tile_counters, uint32_t* dev_err, cudaStream_t s, const char** why) {
     *why = nullptr;
     if (a.M == 0 || a.N == 0) return cudaSuccess;
+    if (reinterpret_cast<uintptr_t>(a.idx) & 15u) { *why = "tcgen05 variant: the index buffer must be 16-byte aligned"; return cudaErrorInvalidValue; }
     UmmaParams p;
     p.a = a;
     p.slabs_total = (uint32_t)(((uint64_t)a.CB * a.CT + kSlabK - 1) / kSlabK);
     uint32_t split = plan.split ? plan.split : 1;
     if (split > p.slabs_total) split = p.slabs_total;
-    p.slabs_per_cta = (p.slabs_total + split - 1) / split;
-    split = (p.slabs_total + p.slabs_per_cta - 1) / p.slabs_per_cta;  // no empty slices
+    p.slabs_per_item = (p.slabs_total + split - 1) / split;
+    split = (p.slabs_total + p.slabs_per_item - 1) / p.slabs_per_item;  // no empty slices
     p.split = split;
-    p.stages = plan.stages ? plan.stages : 4;
+    p.stages = plan.stages ? plan.stages : default_stages(plan.n_tile);
     if (p.stages > kMaxStages) p.stages = kMaxStages;
     if (p.stages < 2) p.stages = 2;
-    while (p.stages > 2 && umma_smem_bytes(plan.n_tile, p.stages) > 227 * 1024) --p.stages;
+    while (p.stages > 2 && umma_smem_bytes(plan.n_tile, p.stages) > kSmemLimit) --p.stages;
+    p.tiles_m = (a.M + kMTile - 1) / kMTile;
+    p.tiles_n = (a.N + plan.n_tile - 1) / plan.n_tile;
+    p.log2_ct = 0;
+    while ((1u << p.log2_ct) < a.CT) ++p.log2_ct;
     p.acc_scratch = acc_scratch;
     p.tile_counters = tile_counters;
     p.dev_err = dev_err;
     if (split > 1 && (!acc_scratch || !tile_counters)) { *why = "tcgen05 variant: split > 1 needs scratch"; return cudaErrorInvalidValue; }
     const size_t smem = umma_smem_bytes(plan.n_tile, p.stages);
-    dim3 grid((a.N + plan.n_tile - 1) / plan.n_tile, (a.M + kMTile - 1) / kMTile, split);
+    const uint64_t items = (uint64_t)p.tiles_m * p.tiles_n * split;
+    const uint32_t cap = plan.max_ctas ? plan.max_ctas : 148u;
+    const uint32_t grid = (uint32_t)(items < cap ? items : cap);
     switch (plan.n_tile) {
         case 64: return run<64>(lut_t_map, p, grid, smem, s);
         case 128: return run<128>(lut_t_map, p, grid, smem, s);

@@ -191,22 +191,13 @@ int run_lut(lutamm_ctx* c, Layer& L, const uint8_t* d_idx, float* d_out, int32_t
     if (variant == LUTAMM_VARIANT_AUTO) variant = resolve_variant(c, L);
     if (variant == LUTAMM_VARIANT_UMMA) {
         if (!umma_supported(L.CB, L.CT, L.N))
-            return fail(c, LUTAMM_EUNSUPPORTED, "tcgen05 variant does not cover this shape (num_centroid must be a power of two in 8..256)");
+            return fail(c, LUTAMM_EUNSUPPORTED, "tcgen05 variant does not cover this shape (num_centroid a power of two in 8..256, num_codebook % 16 == 0)");
         UmmaPlan up;
         umma_default_plan(M, L.CB, L.CT, L.N, c->sm_count, &up);
-        if (plan.umma_n_tile) up.n_tile = plan.umma_n_tile;
-        if (plan.umma_n_tile && !plan.umma_split) {
-            // recompute the split for the forced tile
-            UmmaPlan tmp = up;
-            const uint32_t tiles = ((M + 127) / 128) * ((L.N + up.n_tile - 1) / up.n_tile);
-            const uint32_t slabs = (uint32_t)(((uint64_t)L.CB * L.CT + 127) / 128);
-            uint32_t split = tiles < (uint32_t)c->sm_count ? (uint32_t)c->sm_count / tiles : 1;
-            const uint32_t max_split = slabs / 8 ? slabs / 8 : 1;
-            if (split > max_split) split = max_split;
-            if (split > 16) split = 16;
-            tmp.split = split ? split : 1;
-            tmp.stages = up.n_tile == 256 ? 4 : (up.n_tile == 128 ? 6 : 8);
-            up = tmp;
+        if (plan.umma_n_tile) {
+            up.n_tile = plan.umma_n_tile;
+            up.split = umma_auto_split(M, L.CB, L.CT, L.N, up.n_tile, c->sm_count);
+            up.stages = 0;  // largest pipeline that fits
         }
         if (plan.umma_split) up.split = plan.umma_split;
         if (plan.umma_stages) up.stages = plan.umma_stages;

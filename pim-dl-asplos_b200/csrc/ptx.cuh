@@ -48,6 +48,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // Bounded wait.  `abort_word` is a shared-memory word any role sets once something went
 // wrong; every waiter polls it so one failure releases the whole CTA.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_word) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_word) return false;
     for (uint32_t it = 0; it < kWaitLimit; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((it & 63u) == 63u && *abort_word) return false;

@@ -15,9 +15,9 @@ pytestmark = pytest.mark.gpu
 RTOL = 1e-5  # the tolerance the task states for dequantised fp32 outputs
 
 
-def variants_for(CT, N):
+def variants_for(CT, N, CB=16):
     v = [("gather", dict(variant=P.VARIANT_GATHER, gather_cfg=c)) for c in range(5)]
-    if CT in (8, 16, 32, 64, 128, 256) and N % 16 == 0:
+    if CT in (8, 16, 32, 64, 128, 256) and N % 16 == 0 and CB % 16 == 0:
         v += [("umma128", dict(variant=P.VARIANT_UMMA, umma_n_tile=128, umma_split=1)),
               ("umma256", dict(variant=P.VARIANT_UMMA, umma_n_tile=256, umma_split=1)),
               ("umma64s", dict(variant=P.VARIANT_UMMA, umma_n_tile=64, umma_split=2)),
@@ -34,7 +34,7 @@ def check_case(ctx, x, centroid, lut, bias, scale, lut_bias, want=None, plans=No
     else:
         out, idx, acc = want
     ctx.load_weights(layer_id, centroid, lut, bias, scale, lut_bias)
-    for name, plan in (plans or variants_for(CT, N)):
+    for name, plan in (plans or variants_for(CT, N, CB)):
         ctx.set_plan(layer_id, **plan)
         g_out, g_idx, g_acc = ctx.amm_debug(layer_id, np.ascontiguousarray(x))
         assert np.array_equal(g_idx, idx.astype(np.uint8)), f"{name}: indices differ"
