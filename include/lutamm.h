@@ -93,10 +93,12 @@ typedef struct lutamm_plan {
     uint32_t variant;         /* LUTAMM_VARIANT_*                                         */
     uint32_t ccs_tokens;      /* tokens each search thread walks (0 = default)            */
     uint32_t gather_cfg;      /* gather kernel tile configuration id (0 = default)        */
-    uint32_t umma_n_tile;     /* tcgen05 N tile: 64, 128 or 256 (0 = default)             */
+    uint32_t umma_n_tile;     /* tcgen05 N tile: 64, 128, 192 or 256 (0 = default)        */
     uint32_t umma_split;      /* tcgen05 split of the codebook axis across CTAs (0 = auto) */
-    uint32_t umma_stages;     /* tcgen05 shared-memory pipeline depth (0 = default)       */
-    uint32_t reserved[2];
+    uint32_t umma_stages;     /* tcgen05 pipeline depth (0 = as deep as fits)             */
+    uint32_t umma_groups;     /* tcgen05 one-hot builder groups of 4 warps (0 = default)  */
+    uint32_t umma_operand;    /* where the one-hot operand lives: 0 = default,
+                                 1 = shared memory, 2 = tensor memory (TMEM)             */
 } lutamm_plan;
 
 /* Device times of the last timed call, milliseconds (CUDA events on the context's stream).

@@ -29,11 +29,6 @@ namespace {
 constexpr float kEps = 1e-6f;  // (double)diff > 1e-6  <=>  diff > 1e-6f for fp32 diff
 
 template <int V>
-struct XVec {
-    float f[V];
-};
-
-template <int V>
 __device__ __forceinline__ void load_x(const float* __restrict__ p, float (&f)[V]) {
     if constexpr (V % 4 == 0) {
 #pragma unroll
@@ -64,14 +59,29 @@ __device__ __forceinline__ size_t tiled_index_offset(uint32_t m, uint32_t cb, ui
 // ------------------------------------------------------------------ reg path
 constexpr int kRegThreads = 128;
 
+// kTok tokens are in flight per thread: their activations are loaded together (one round
+// trip to memory instead of kTok) and their scans interleave, which gives the scheduler
+// kTok independent dependency chains per warp.
+constexpr int kTok = 4;
+
 template <int V, int CT, bool TILED>
 __global__ void __launch_bounds__(kRegThreads)
 ccs_reg_kernel(const float* __restrict__ x, const float* __restrict__ cent, void* __restrict__ out, uint32_t M,
                uint32_t K, uint32_t CB, uint32_t tokens_per_cta, uint32_t n_stile, uint32_t cb_mtile) {
+    // Let the kernel queued behind this one (the LUT kernel) start its prologue - barrier
+    // set-up, tensor-memory allocation, the first LUT tiles - while the search runs; it
+    // waits for this grid to finish before it touches the indices.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const uint32_t cb = blockIdx.x * kRegThreads + threadIdx.x;
     if (cb >= CB) return;
     const uint32_t m0 = blockIdx.y * tokens_per_cta;
     const uint32_t m1 = min(M, m0 + tokens_per_cta);
+
+    // first batch of activations before the centroids, so both round trips overlap
+    float xs[kTok][V];
+    const float* xp = x + (size_t)cb * V;
+#pragma unroll
+    for (int t = 0; t < kTok; ++t) load_x<V>(xp + (size_t)min(m0 + t, M - 1) * K, xs[t]);
 
     float c[CT][V];
     {
@@ -85,33 +95,48 @@ ccs_reg_kernel(const float* __restrict__ x, const float* __restrict__ cent, void
         }
     }
 
-    const float* xp = x + (size_t)m0 * K + (size_t)cb * V;
-#pragma unroll 2
-    for (uint32_t m = m0; m < m1; ++m, xp += K) {
-        float xs[V];
-        load_x<V>(xp, xs);
-        float mn = 0.f;
-        uint32_t best = 0;
+    for (uint32_t m = m0; m < m1; m += kTok) {
+        float cur[kTok][V];
+#pragma unroll
+        for (int t = 0; t < kTok; ++t)
+#pragma unroll
+            for (int d = 0; d < V; ++d) cur[t][d] = xs[t][d];
+        if (m + kTok < m1) {  // next batch while this one is scanned
+#pragma unroll
+            for (int t = 0; t < kTok; ++t) load_x<V>(xp + (size_t)min(m + kTok + t, M - 1) * K, xs[t]);
+        }
+        float mn[kTok];
+        uint32_t best[kTok];
 #pragma unroll
         for (int ct = 0; ct < CT; ++ct) {
-            float t = 0.f;
 #pragma unroll
-            for (int d = 0; d < V; ++d) {
-                float e = __fsub_rn(xs[d], c[ct][d]);
-                t = __fadd_rn(t, __fmul_rn(e, e));
-            }
-            if (ct == 0) {
-                mn = t;
-            } else {
-                bool take = __fsub_rn(mn, t) > kEps;  // false for NaN: keeps the earlier index
-                mn = take ? t : mn;
-                best = take ? (uint32_t)ct : best;
+            for (int t = 0; t < kTok; ++t) {
+                float acc = 0.f;
+#pragma unroll
+                for (int d = 0; d < V; ++d) {
+                    float e = __fsub_rn(cur[t][d], c[ct][d]);
+                    acc = __fadd_rn(acc, __fmul_rn(e, e));
+                }
+                if (ct == 0) {
+                    mn[t] = acc;
+                    best[t] = 0;
+                } else {
+                    bool take = __fsub_rn(mn[t], acc) > kEps;  // false for NaN: keeps the earlier index
+                    mn[t] = take ? acc : mn[t];
+                    best[t] = take ? (uint32_t)ct : best[t];
+                }
             }
         }
-        if constexpr (TILED) {
-            reinterpret_cast<uint16_t*>(out)[tiled_index_offset(m, cb, CB, n_stile, cb_mtile)] = (uint16_t)best;
-        } else {
-            reinterpret_cast<uint8_t*>(out)[(size_t)m * CB + cb] = (uint8_t)best;
+#pragma unroll
+        for (int t = 0; t < kTok; ++t) {
+            const uint32_t mm = m + t;
+            if (mm < m1) {
+                if constexpr (TILED) {
+                    reinterpret_cast<uint16_t*>(out)[tiled_index_offset(mm, cb, CB, n_stile, cb_mtile)] = (uint16_t)best[t];
+                } else {
+                    reinterpret_cast<uint8_t*>(out)[(size_t)mm * CB + cb] = (uint8_t)best[t];
+                }
+            }
         }
     }
 }
@@ -127,6 +152,7 @@ ccs_smem_kernel(const float* __restrict__ x, const float* __restrict__ cent, voi
                 uint32_t K, uint32_t v_rt, uint32_t CB, uint32_t CT, uint32_t cb_per_cta, uint32_t n_stile,
                 uint32_t cb_mtile) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // see ccs_reg_kernel
     const uint32_t v = V > 0 ? (uint32_t)V : v_rt;
     float* s_cent = reinterpret_cast<float*>(smem_raw);                   // [cbs][CT][v]
     const uint32_t cb0 = blockIdx.x * cb_per_cta;
@@ -193,7 +219,17 @@ ccs_smem_kernel(const float* __restrict__ x, const float* __restrict__ cent, voi
 
 template <int V, int CT>
 cudaError_t run_reg(const CcsArgs& a, cudaStream_t s) {
-    uint32_t tpt = a.tokens_per_thread ? a.tokens_per_thread : 16u;
+    // Default run length per thread: long enough to amortise the centroid load, short enough
+    // that a small batch still spreads over the whole GPU (about 8 CTAs of 4 warps per SM).
+    uint32_t tpt = a.tokens_per_thread;
+    if (!tpt) {
+        const uint64_t cb_blocks = (a.CB + kRegThreads - 1) / kRegThreads;
+        const uint64_t want_ctas = 148ull * 8ull;
+        tpt = (uint32_t)((a.M * cb_blocks + want_ctas - 1) / want_ctas);
+        if (tpt < (uint32_t)kTok) tpt = kTok;
+        if (tpt > 64u) tpt = 64u;
+    }
+    tpt = (tpt + kTok - 1) / kTok * kTok;
     dim3 grid((a.CB + kRegThreads - 1) / kRegThreads, (a.M + tpt - 1) / tpt);
     if (a.format == LUTAMM_INDEX_U16_TILED)
         ccs_reg_kernel<V, CT, true><<<grid, kRegThreads, 0, s>>>(a.x, a.centroid, a.idx_out, a.M, a.K, a.CB, tpt,

@@ -49,18 +49,22 @@ cudaError_t launch_gather(const LutArgs& a, const CUtensorMap& lut_map, uint32_t
 // tcgen05 variant: LUT transposed to K-major [N][CB*CT] at load time, 2-D TMA tiles with
 // 128-byte swizzle; the one-hot operand is synthesised in shared memory from the indices.
 struct UmmaPlan {
-    uint32_t n_tile;  // 64 / 128 / 256
-    uint32_t split;   // CTAs sharing one output tile along the codebook axis
-    uint32_t stages;
+    uint32_t n_tile;    // 64 / 128 / 256 (A in shared memory), 64 / 128 / 192 (A in tensor memory)
+    uint32_t a_tmem;    // 1: the one-hot operand is written to tensor memory instead of shared memory
+    uint32_t split;     // work items sharing one output tile along the codebook axis
+    uint32_t stages;    // 0 = as many as fit
+    uint32_t groups;    // one-hot builder groups of four warps (0 = default)
+    uint32_t sps;       // 128-byte slabs of the contraction axis per pipeline stage: 1, 2 (default) or 4
     uint32_t max_ctas;  // persistent grid size cap: the SM count
 };
 bool umma_supported(uint32_t CB, uint32_t CT, uint32_t N);
+bool umma_tile_ok(uint32_t n_tile, bool a_tmem);
 cudaError_t umma_make_tmap(CUtensorMap* out, const int8_t* lut_t, uint32_t CB, uint32_t CT, uint32_t N,
                            uint32_t n_tile, const char** why);
-// `acc_scratch` (int32 [M][N]) and `tile_counters` are needed when split > 1.
+// `acc_scratch` (int32 [split][M][N]) and `tile_counters` (zeroed once) are needed when split > 1.
 cudaError_t launch_umma(const LutArgs& a, const CUtensorMap& lut_t_map, const UmmaPlan& p, int32_t* acc_scratch,
                         uint32_t* tile_counters, uint32_t* dev_err, cudaStream_t s, const char** why);
-void umma_default_plan(uint32_t M, uint32_t CB, uint32_t CT, uint32_t N, int sm_count, UmmaPlan* p);
+void umma_default_plan(uint32_t M, uint32_t CB, uint32_t CT, uint32_t N, int sm_count, bool a_tmem, UmmaPlan* p);
 uint32_t umma_auto_split(uint32_t M, uint32_t CB, uint32_t CT, uint32_t N, uint32_t n_tile, int sm_count);
 
 // LUT [CB*CT][N] -> [N][CB*CT]

@@ -12,8 +12,8 @@
 //
 // Persistent kernel: one CTA per SM walks a list of work items, an item being one
 // 128-token x N_TILE-column output tile, or one slice of its contraction axis when
-// split > 1 (partial sums then meet in an int32 scratch tile in L2 through coalesced
-// red.add, and the CTA that arrives last dequantises the tile and re-zeroes the scratch).
+// split > 1 (each slice then writes its int32 partial tile to scratch in L2 with plain
+// stores, and the CTA that arrives last at a tile sums the slices and dequantises).
 // The accumulator is double-buffered in TMEM so the epilogue of one item overlaps the
 // main loop of the next.
 //
@@ -42,11 +42,11 @@ namespace {
 constexpr uint32_t kMTile = 128;
 constexpr uint32_t kSlabK = 128;               // bytes of K per pipeline stage = one swizzle row
 constexpr uint32_t kABytes = kMTile * kSlabK;  // 16 KiB
-constexpr uint32_t kAgenGroups = 4;  // each group: 4 warps = 128 rows
-constexpr uint32_t kAgenWarps = 4 * kAgenGroups, kEpiWarps = 4;
+constexpr uint32_t kMaxAgenGroups = 6;  // each group: 4 warps = 128 rows
+constexpr uint32_t kEpiWarps = 4;
 constexpr uint32_t kEpiThreads = kEpiWarps * 32;
-constexpr uint32_t kFirstAgenWarp = 2, kFirstEpiWarp = kFirstAgenWarp + kAgenWarps;
-constexpr uint32_t kThreads = (kFirstEpiWarp + kEpiWarps) * 32;  // 704
+constexpr uint32_t kFirstAgenWarp = 2;
+constexpr uint32_t kMaxThreads = (kFirstAgenWarp + 4 * kMaxAgenGroups + kEpiWarps) * 32;  // 960
 constexpr uint32_t kMaxStages = 8;
 constexpr uint32_t kStageWarpBytes = 32 * 128;           // epilogue transpose buffer per warp
 
@@ -58,7 +58,8 @@ struct UmmaParams {
     uint32_t stages;
     uint32_t tiles_m, tiles_n;
     uint32_t log2_ct;
-    int32_t* acc_scratch;    // [M][N] int32, all zero between launches (split > 1)
+    uint32_t groups;         // A-builder groups (1..6)
+    int32_t* acc_scratch;    // [split][M][N] int32 partial sums (split > 1); needs no initialisation
     uint32_t* tile_counters;
     uint32_t* dev_err;
 };
@@ -74,12 +75,13 @@ __device__ __forceinline__ uint4 onehot16(uint32_t i) {
 }
 
 struct Item {
-    uint32_t m0, n0, slab_begin, nslab, tile;
+    uint32_t m0, n0, slab_begin, nslab, tile, z;
 };
 __device__ __forceinline__ Item decode_item(const UmmaParams& p, uint32_t item, uint32_t n_tile) {
     Item it;
     const uint32_t z = item % p.split, tile = item / p.split;
     it.tile = tile;
+    it.z = z;
     it.m0 = (tile % p.tiles_m) * kMTile;
     it.n0 = (tile / p.tiles_m) * n_tile;
     it.slab_begin = z * p.slabs_per_item;
@@ -88,19 +90,24 @@ __device__ __forceinline__ Item decode_item(const UmmaParams& p, uint32_t item, 
     return it;
 }
 
-template <uint32_t N_TILE>
-__global__ void __launch_bounds__(kThreads, 1)
+template <uint32_t N_TILE, bool A_TMEM, uint32_t SPS>
+__global__ void __launch_bounds__(kMaxThreads, 1)
 lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const UmmaParams p) {
     constexpr uint32_t kBBytes = N_TILE * kSlabK;
     constexpr uint32_t kIdesc = umma_idesc_i8(kMTile, N_TILE, /*a_signed=*/1, /*b_signed=*/1);
-    constexpr uint32_t kTmemCols = 2 * N_TILE < 32 ? 32 : 2 * N_TILE;  // two accumulators
+    // Tensor memory: two accumulators of N_TILE columns; with A_TMEM also the ring of one-hot
+    // A slabs (32 columns = 128 bytes of K per row) behind them.
+    constexpr uint32_t kTmemCols = A_TMEM ? 512u : (2 * N_TILE <= 32 ? 32u : 2 * N_TILE <= 64 ? 64u : 2 * N_TILE <= 128 ? 128u : 2 * N_TILE <= 256 ? 256u : 512u);
+    constexpr uint32_t kATmemBase = 2 * N_TILE;
+    constexpr uint32_t kAStageBytes = A_TMEM ? 0u : SPS * kABytes;
+    constexpr uint32_t kBStageBytes = SPS * kBBytes;
 
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     const uint32_t S = p.stages;
-    unsigned char* s_a = smem;                                   // [S][16 KiB], 1024-aligned
-    unsigned char* s_b = s_a + (size_t)S * kABytes;              // [S][N_TILE*128], 1024-aligned
-    unsigned char* s_stage = s_b + (size_t)S * kBBytes;          // [4][32][128] epilogue transpose
+    unsigned char* s_a = smem;                                   // [S][SPS][16 KiB], 1024-aligned
+    unsigned char* s_b = s_a + (size_t)S * kAStageBytes;         // [S][SPS][N_TILE*128], 1024-aligned
+    unsigned char* s_stage = s_b + (size_t)S * kBStageBytes;     // [4][32][128] epilogue transpose
     uint64_t* s_bar = reinterpret_cast<uint64_t*>(s_stage + kEpiWarps * kStageWarpBytes);
     uint32_t* s_misc = reinterpret_cast<uint32_t*>(s_bar + 2 * kMaxStages + 4);  // tmem base, abort, last
     volatile uint32_t* s_abort = s_misc + 1;
@@ -111,12 +118,14 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
     const LutArgs& a = p.a;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t n_items = p.tiles_m * p.tiles_n * p.split;
+    const uint32_t kAgenGroups = p.groups;
+    const uint32_t kFirstEpiWarp = kFirstAgenWarp + 4 * kAgenGroups;
 
     if (threadIdx.x == 0) {
         s_misc[0] = 0; s_misc[1] = 0; s_misc[2] = 0;
         for (uint32_t s = 0; s < S; ++s) {
-            mbar_init(full0 + 8 * s, 4 + 1);           // the four warps of one A-builder group + the TMA
-            mbar_init(empty0 + 8 * s, 1);              // tcgen05.commit
+            mbar_init(full0 + 8 * s, SPS * 4 + 1);  // four builder warps per slab of the stage + the TMA
+            mbar_init(empty0 + 8 * s, 1);            // tcgen05.commit
         }
         for (uint32_t b = 0; b < 2; ++b) {
             mbar_init(acc_full0 + 8 * b, 1);           // tcgen05.commit
@@ -135,20 +144,27 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
     tc_fence_after_sync();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(s_misc);
 
+    // A "round" is one pipeline stage's worth of the contraction axis: SPS slabs of 128 bytes,
+    // 4*SPS tcgen05.mma between one wait and one commit.  The commit/wait round trip costs a
+    // few hundred cycles on the issuing thread whatever the stage holds, so a stage has to
+    // hold enough math to hide it.
     if (warp == 0) {
         // ---------------- TMA producer (the LUT never depends on the preceding kernel)
         if (lane == 0) {
-            uint32_t g = 0;
+            uint32_t s = 0, ph = 0;  // stage and phase bit of the current round
             bool ok = true;
             for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
                 const Item it = decode_item(p, item, N_TILE);
-                for (uint32_t i = 0; i < it.nslab; ++i, ++g) {
-                    const uint32_t s = g % S, ph = (g / S) & 1;
+                const uint32_t rounds = (it.nslab + SPS - 1) / SPS;
+                for (uint32_t rr = 0; rr < rounds; ++rr) {
                     ok = mbar_wait(empty0 + 8 * s, ph ^ 1, s_abort);
                     if (!ok) break;
-                    mbar_arrive_expect_tx(full0 + 8 * s, kBBytes);
-                    tma_load_2d(smem_u32(s_b + (size_t)s * kBBytes), &lut_t_map, full0 + 8 * s,
-                                (int32_t)((it.slab_begin + i) * kSlabK), (int32_t)it.n0);
+                    const uint32_t valid = min(SPS, it.nslab - rr * SPS);
+                    mbar_arrive_expect_tx(full0 + 8 * s, valid * kBBytes);
+                    for (uint32_t h = 0; h < valid; ++h)
+                        tma_load_2d(smem_u32(s_b + (size_t)(s * SPS + h) * kBBytes), &lut_t_map, full0 + 8 * s,
+                                    (int32_t)((it.slab_begin + rr * SPS + h) * kSlabK), (int32_t)it.n0);
+                    if (++s == S) { s = 0; ph ^= 1; }
                 }
             }
         }
@@ -156,42 +172,56 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
     } else if (warp == 1) {
         // ---------------- MMA issuer
         if (lane == 0) {
-            uint32_t g = 0, t = 0;
+            uint32_t s = 0, ph = 0, t = 0;
             bool ok = true;
             for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++t) {
                 const Item it = decode_item(p, item, N_TILE);
+                const uint32_t rounds = (it.nslab + SPS - 1) / SPS;
                 const uint32_t ab = t & 1, aph = (t >> 1) & 1;
                 ok = mbar_wait(acc_empty0 + 8 * ab, aph ^ 1, s_abort);  // epilogue drained this buffer
                 if (!ok) break;
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + ab * N_TILE;
-                for (uint32_t i = 0; i < it.nslab; ++i, ++g) {
-                    const uint32_t s = g % S, ph = (g / S) & 1;
+                for (uint32_t rr = 0; rr < rounds; ++rr) {
                     ok = mbar_wait(full0 + 8 * s, ph, s_abort);
                     if (!ok) break;
                     tc_fence_after_sync();
-                    const uint64_t da = umma_desc_k_sw128(smem_u32(s_a + (size_t)s * kABytes));
-                    const uint64_t db = umma_desc_k_sw128(smem_u32(s_b + (size_t)s * kBBytes));
+                    const uint32_t valid = min(SPS, it.nslab - rr * SPS);
 #pragma unroll
-                    for (uint32_t kk = 0; kk < kSlabK / 32; ++kk)  // 32 bytes of K per instruction
-                        umma_i8(d_tmem, da + 2 * kk, db + 2 * kk, kIdesc, (i | kk) != 0 ? 1u : 0u);
+                    for (uint32_t h = 0; h < SPS; ++h) {
+                        if (h < valid) {
+                            const uint64_t db = umma_desc_k_sw128(smem_u32(s_b + (size_t)(s * SPS + h) * kBBytes));
+                            if constexpr (A_TMEM) {
+                                const uint32_t ta = tmem_base + kATmemBase + (s * SPS + h) * 32;
+#pragma unroll
+                                for (uint32_t kk = 0; kk < kSlabK / 32; ++kk)  // 32 bytes of K = 8 TMEM columns of A
+                                    umma_i8_ts(d_tmem, ta + 8 * kk, db + 2 * kk, kIdesc, (rr | h | kk) != 0 ? 1u : 0u);
+                            } else {
+                                const uint64_t da = umma_desc_k_sw128(smem_u32(s_a + (size_t)(s * SPS + h) * kABytes));
+#pragma unroll
+                                for (uint32_t kk = 0; kk < kSlabK / 32; ++kk)  // 32 bytes of K per instruction
+                                    umma_i8(d_tmem, da + 2 * kk, db + 2 * kk, kIdesc, (rr | h | kk) != 0 ? 1u : 0u);
+                            }
+                        }
+                    }
                     umma_commit(empty0 + 8 * s);  // frees the stage once these MMAs have read it
+                    if (++s == S) { s = 0; ph ^= 1; }
                 }
                 if (ok) umma_commit(acc_full0 + 8 * ab);
             }
         }
         __syncwarp();
     } else if (warp < kFirstEpiWarp) {
-        // ---------------- one-hot A builders: kAgenGroups groups of 4 warps; group k owns
-        // every kAgenGroups-th slab of the CTA's slab sequence, one tile row per thread, so
-        // the fixed latencies of a slab (index load, wait, proxy fence, arrive) overlap
-        // across groups instead of adding up.
+        // ---------------- one-hot A builders: groups of 4 warps; group k owns every
+        // kAgenGroups-th slab of the CTA's slab sequence, one tile row per thread, so the
+        // fixed latencies of a slab (index load, wait, fence, arrive) overlap across groups
+        // instead of adding up.
         // The indices come from the kernel launched just before; ld.global.cg reads them from
         // L2, which matters because under programmatic dependent launch this CTA may have
         // started, on an SM with older lines in L1, before that kernel finished.
         pdl_wait_prior_grid();
         const uint32_t grp = (warp - kFirstAgenWarp) >> 2;
-        const uint32_t r = (warp & 3u) * 32 + lane;  // tile row
+        const uint32_t r = (warp & 3u) * 32 + lane;  // tile row == TMEM lane
         const uint32_t sw = r & 7u;
         const uint32_t CT = a.CT, lg = p.log2_ct;
         // bytes of index one slab needs per row: 128 / CT codebooks (at least one byte)
@@ -205,15 +235,18 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
             else v.x = __ldcg(q);
             return v;
         };
-        uint32_t g = 0;
+        uint32_t g = 0;  // slab counter of the CTA, items padded to whole rounds
         bool ok = true;
         for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
             const Item it = decode_item(p, item, N_TILE);
+            const uint32_t padded = ((it.nslab + SPS - 1) / SPS) * SPS;
             const uint8_t* grow = a.idx + (size_t)min(it.m0 + r, a.M - 1) * a.CB;  // rows past M: masked in the epilogue
             uint32_t i = (grp + kAgenGroups - (g % kAgenGroups)) % kAgenGroups;
+            // round, stage and phase bit of slab g + i; advanced incrementally below
+            uint32_t R = (g + i) / SPS, s = R % S, ph = (R / S) & 1;
             uint4 raw_next = make_uint4(0, 0, 0, 0);
             if (i < it.nslab) raw_next = load_raw(grow, it.slab_begin + i);
-            for (; i < it.nslab && ok; i += kAgenGroups) {
+            for (; i < padded && ok; i += kAgenGroups) {
                 const uint32_t slab = it.slab_begin + i;
                 const uint4 raw = raw_next;
                 if (i + kAgenGroups < it.nslab) raw_next = load_raw(grow, slab + kAgenGroups);
@@ -239,23 +272,40 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
                         chunk[j] = onehot16((ix >> 4) == sub ? (ix & 15u) : 16u);
                     }
                 }
-                const uint32_t gg = g + i, s = gg % S, ph = (gg / S) & 1;
+                const uint32_t gg = g + i, h = gg % SPS;
+                for (const uint32_t Rn = gg / SPS; R < Rn; ++R)
+                    if (++s == S) { s = 0; ph ^= 1; }
                 uint32_t w_ok = 1;
                 if (lane == 0) w_ok = mbar_wait(empty0 + 8 * s, ph ^ 1, s_abort) ? 1u : 0u;
                 ok = __shfl_sync(0xffffffffu, w_ok, 0) != 0;
                 if (!ok) break;
-                unsigned char* row_ptr = s_a + (size_t)s * kABytes + r * kSlabK;
+                if (i < it.nslab) {  // padding slabs of a last, partial round only arrive
+                    if constexpr (A_TMEM) {
+                        // the row goes to this warp's lane quadrant of tensor memory, K bytes in column order
+                        uint32_t w[32];
 #pragma unroll
-                for (uint32_t j = 0; j < 8; ++j)  // 128-byte swizzle: 16-byte chunk j of row r lands at j ^ (r & 7)
-                    *reinterpret_cast<uint4*>(row_ptr + ((j ^ sw) << 4)) = chunk[j];
-                fence_proxy_async_smem();
+                        for (uint32_t j = 0; j < 8; ++j) {
+                            w[4 * j + 0] = chunk[j].x; w[4 * j + 1] = chunk[j].y; w[4 * j + 2] = chunk[j].z; w[4 * j + 3] = chunk[j].w;
+                        }
+                        tc_fence_after_sync();
+                        tmem_st_32x32b_x32(tmem_base + (((warp & 3u) * 32u) << 16) + kATmemBase + (s * SPS + h) * 32, w);
+                        tmem_st_wait();
+                        tc_fence_before_sync();
+                    } else {
+                        unsigned char* row_ptr = s_a + (size_t)(s * SPS + h) * kABytes + r * kSlabK;
+#pragma unroll
+                        for (uint32_t j = 0; j < 8; ++j)  // 128-byte swizzle: 16-byte chunk j of row r lands at j ^ (r & 7)
+                            *reinterpret_cast<uint4*>(row_ptr + ((j ^ sw) << 4)) = chunk[j];
+                        fence_proxy_async_smem();
+                    }
+                }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(full0 + 8 * s);
             }
-            g += it.nslab;
+            g += padded;
         }
     } else {
-        // ---------------- epilogue (warps 18..21 -> TMEM lane quadrants 2,3,0,1)
+        // ---------------- epilogue: four warps, each on the TMEM lane quadrant (warp % 4) it may read
         pdl_wait_prior_grid();
         const uint32_t quad = warp & 3u;
         const uint32_t et = threadIdx.x - kFirstEpiWarp * 32;
@@ -297,35 +347,30 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
                             const uint32_t mm = it.m0 + quad * 32 + rr;
                             if (mm >= a.M) continue;
                             const int4 val = *reinterpret_cast<const int4*>(stg + rr * 128 + ((ch ^ (rr & 7u)) << 4));
-                            if (p.split == 1) {
-                                float4 o;
-                                o.x = dequant_one(val.x, a.scale, lbcb, b4.x);
-                                o.y = dequant_one(val.y, a.scale, lbcb, b4.y);
-                                o.z = dequant_one(val.z, a.scale, lbcb, b4.z);
-                                o.w = dequant_one(val.w, a.scale, lbcb, b4.w);
-                                if (!a.layout.tiled) {
-                                    *reinterpret_cast<float4*>(a.out + (size_t)mm * a.N + n) = o;
-                                } else {
-                                    a.out[tiled_out_offset(mm, n + 0, a.layout)] = o.x;
-                                    a.out[tiled_out_offset(mm, n + 1, a.layout)] = o.y;
-                                    a.out[tiled_out_offset(mm, n + 2, a.layout)] = o.z;
-                                    a.out[tiled_out_offset(mm, n + 3, a.layout)] = o.w;
-                                }
-                                if (a.acc_out) *reinterpret_cast<int4*>(a.acc_out + (size_t)mm * a.N + n) = val;
-                            } else {
-                                int32_t* dst = p.acc_scratch + (size_t)mm * a.N + n;
-                                atomicAdd(dst + 0, val.x);
-                                atomicAdd(dst + 1, val.y);
-                                atomicAdd(dst + 2, val.z);
-                                atomicAdd(dst + 3, val.w);
+                            if (p.split > 1) {  // this slice's partial sums, plain row-contiguous stores
+                                __stcg(reinterpret_cast<int4*>(p.acc_scratch + ((size_t)it.z * a.M + mm) * a.N + n), val);
+                                continue;
                             }
+                            float4 o;
+                            o.x = dequant_one(val.x, a.scale, lbcb, b4.x);
+                            o.y = dequant_one(val.y, a.scale, lbcb, b4.y);
+                            o.z = dequant_one(val.z, a.scale, lbcb, b4.z);
+                            o.w = dequant_one(val.w, a.scale, lbcb, b4.w);
+                            if (!a.layout.tiled) {
+                                *reinterpret_cast<float4*>(a.out + (size_t)mm * a.N + n) = o;
+                            } else {
+                                a.out[tiled_out_offset(mm, n + 0, a.layout)] = o.x;
+                                a.out[tiled_out_offset(mm, n + 1, a.layout)] = o.y;
+                                a.out[tiled_out_offset(mm, n + 2, a.layout)] = o.z;
+                                a.out[tiled_out_offset(mm, n + 3, a.layout)] = o.w;
+                            }
+                            if (a.acc_out) *reinterpret_cast<int4*>(a.acc_out + (size_t)mm * a.N + n) = val;
                         }
                     }
                 }
             }
             if (p.split > 1) {
-                // The CTA that arrives last at this output tile dequantises the summed tile and
-                // re-zeroes the scratch.  Every epilogue thread runs the barriers, also after a
+                // The CTA that arrives last at this output tile sums the slices and dequantises.  Every epilogue thread runs the barriers, also after a
                 // failed wait, so nobody is left behind at one.
                 __threadfence();
                 named_bar_sync(1, kEpiThreads);
@@ -342,25 +387,43 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
                 named_bar_sync(1, kEpiThreads);
                 if (s_misc[2]) {
                     __threadfence();
+                    // All loads of a row first, then the stores: the loop is a chain of L2 round
+                    // trips otherwise.
+                    constexpr uint32_t kChunks = N_TILE / 32;
+#pragma unroll 2
                     for (uint32_t pass = 0; pass < 8; ++pass) {
                         const uint32_t mm = it.m0 + quad * 32 + pass * 4 + rsub;
                         if (mm >= a.M) continue;
-                        for (uint32_t c = 0; c < N_TILE / 32; ++c) {
+                        int4 val[kChunks];
+#pragma unroll
+                        for (uint32_t c = 0; c < kChunks; ++c) val[c] = make_int4(0, 0, 0, 0);
+                        for (uint32_t z = 0; z < p.split; ++z) {  // integer sums: the order is immaterial
+                            int4 part[kChunks];
+#pragma unroll
+                            for (uint32_t c = 0; c < kChunks; ++c) {
+                                const uint32_t n = it.n0 + c * 32 + ch * 4;
+                                part[c] = make_int4(0, 0, 0, 0);
+                                if (n < a.N) part[c] = __ldcg(reinterpret_cast<const int4*>(p.acc_scratch + ((size_t)z * a.M + mm) * a.N + n));
+                            }
+#pragma unroll
+                            for (uint32_t c = 0; c < kChunks; ++c) {
+                                val[c].x += part[c].x; val[c].y += part[c].y; val[c].z += part[c].z; val[c].w += part[c].w;
+                            }
+                        }
+#pragma unroll
+                        for (uint32_t c = 0; c < kChunks; ++c) {
                             const uint32_t n = it.n0 + c * 32 + ch * 4;
                             if (n >= a.N) continue;
-                            int4* src = reinterpret_cast<int4*>(p.acc_scratch + (size_t)mm * a.N + n);
-                            const int4 val = __ldcg(src);
-                            __stcg(src, make_int4(0, 0, 0, 0));
                             const float4 b4 = __ldg(reinterpret_cast<const float4*>(a.bias + n));
-                            float o[4] = {dequant_one(val.x, a.scale, lbcb, b4.x), dequant_one(val.y, a.scale, lbcb, b4.y),
-                                          dequant_one(val.z, a.scale, lbcb, b4.z), dequant_one(val.w, a.scale, lbcb, b4.w)};
+                            const float o[4] = {dequant_one(val[c].x, a.scale, lbcb, b4.x), dequant_one(val[c].y, a.scale, lbcb, b4.y),
+                                                dequant_one(val[c].z, a.scale, lbcb, b4.z), dequant_one(val[c].w, a.scale, lbcb, b4.w)};
                             if (!a.layout.tiled) {
                                 *reinterpret_cast<float4*>(a.out + (size_t)mm * a.N + n) = make_float4(o[0], o[1], o[2], o[3]);
                             } else {
 #pragma unroll
                                 for (uint32_t k = 0; k < 4; ++k) a.out[tiled_out_offset(mm, n + k, a.layout)] = o[k];
                             }
-                            if (a.acc_out) *reinterpret_cast<int4*>(a.acc_out + (size_t)mm * a.N + n) = val;
+                            if (a.acc_out) *reinterpret_cast<int4*>(a.acc_out + (size_t)mm * a.N + n) = val[c];
                         }
                     }
                 }
@@ -388,20 +451,20 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
     }
 }
 
-size_t umma_smem_bytes(uint32_t n_tile, uint32_t stages) {
-    return (size_t)stages * (kABytes + n_tile * kSlabK) + kEpiWarps * kStageWarpBytes +
+size_t umma_smem_bytes(uint32_t n_tile, uint32_t stages, bool a_tmem, uint32_t sps) {
+    return (size_t)stages * sps * ((a_tmem ? 0 : kABytes) + n_tile * kSlabK) + kEpiWarps * kStageWarpBytes +
            (2 * kMaxStages + 4) * 8 + 16 + 1024;
 }
 constexpr size_t kSmemLimit = 227 * 1024;
 
-template <uint32_t N_TILE>
+template <uint32_t N_TILE, bool A_TMEM, uint32_t SPS>
 cudaError_t run(const CUtensorMap& map, const UmmaParams& p, uint32_t grid, size_t smem, cudaStream_t s) {
-    auto k = lut_onehot_umma_kernel<N_TILE>;
+    auto k = lut_onehot_umma_kernel<N_TILE, A_TMEM, SPS>;
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(kThreads);
+    cfg.blockDim = dim3((kFirstAgenWarp + 4 * p.groups + kEpiWarps) * 32);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = s;
     cudaLaunchAttribute attr[1];
@@ -412,19 +475,31 @@ cudaError_t run(const CUtensorMap& map, const UmmaParams& p, uint32_t grid, size
     return cudaLaunchKernelEx(&cfg, k, map, p);
 }
 
-uint32_t default_stages(uint32_t n_tile) {
+// A in tensor memory: 512 columns hold two accumulators and the A ring, 32 columns a slab.
+uint32_t max_stages(uint32_t n_tile, bool a_tmem, uint32_t sps) {
     uint32_t st = kMaxStages;
-    while (st > 2 && umma_smem_bytes(n_tile, st) > kSmemLimit) --st;
+    if (a_tmem) {
+        const uint32_t room = (512u - 2 * n_tile) / (32u * sps);
+        if (st > room) st = room;
+    }
+    while (st > 1 && umma_smem_bytes(n_tile, st, a_tmem, sps) > kSmemLimit) --st;
     return st;
+}
+bool tile_ok(uint32_t n_tile, bool a_tmem) {
+    if (a_tmem) return n_tile == 64 || n_tile == 128 || n_tile == 192;
+    return n_tile == 64 || n_tile == 128 || n_tile == 256;
 }
 
 }  // namespace
 
 bool umma_supported(uint32_t CB, uint32_t CT, uint32_t N) {
     const bool ct_ok = CT == 8 || CT == 16 || CT == 32 || CT == 64 || CT == 128 || CT == 256;
-    // CB % 16: the index tile is staged in 16-byte pieces; it also makes CB*CT a multiple of 128
+    // CB % 16: a thread reads its row's indices with aligned vector loads; it also makes
+    // CB*CT a multiple of 128, so there is no ragged slab
     return ct_ok && CB > 0 && CB % 16 == 0 && N > 0 && N % 16 == 0;
 }
+
+bool umma_tile_ok(uint32_t n_tile, bool a_tmem) { return tile_ok(n_tile, a_tmem); }
 
 uint32_t umma_auto_split(uint32_t M, uint32_t CB, uint32_t CT, uint32_t N, uint32_t n_tile, int sm_count) {
     const uint32_t slabs = (uint32_t)(((uint64_t)CB * CT + kSlabK - 1) / kSlabK);
@@ -440,11 +515,16 @@ uint32_t umma_auto_split(uint32_t M, uint32_t CB, uint32_t CT, uint32_t N, uint3
     return split;
 }
 
-void umma_default_plan(uint32_t M, uint32_t CB, uint32_t CT, uint32_t N, int sm_count, UmmaPlan* p) {
-    uint32_t n_tile = N >= 256 ? 256 : (N > 64 ? 128 : 64);
+void umma_default_plan(uint32_t M, uint32_t CB, uint32_t CT, uint32_t N, int sm_count, bool a_tmem, UmmaPlan* p) {
+    uint32_t n_tile;
+    if (a_tmem) n_tile = N >= 192 ? 192 : (N > 64 ? 128 : 64);
+    else n_tile = N >= 256 ? 256 : (N > 64 ? 128 : 64);
     p->n_tile = n_tile;
+    p->a_tmem = a_tmem ? 1u : 0u;
     p->split = umma_auto_split(M, CB, CT, N, n_tile, sm_count);
-    p->stages = default_stages(n_tile);
+    p->stages = 0;
+    p->groups = 0;
+    p->sps = 0;
     p->max_ctas = (uint32_t)sm_count;
 }
 
@@ -452,7 +532,7 @@ cudaError_t umma_make_tmap(CUtensorMap* out, const int8_t* lut_t, uint32_t CB, u
                            uint32_t n_tile, const char** why) {
     *why = nullptr;
     if (!umma_supported(CB, CT, N)) { *why = "tcgen05 variant: needs num_centroid in {8,16,32,64,128,256}, num_codebook % 16 == 0, N % 16 == 0"; return cudaErrorInvalidValue; }
-    if (n_tile != 64 && n_tile != 128 && n_tile != 256) { *why = "tcgen05 variant: N tile must be 64, 128 or 256"; return cudaErrorInvalidValue; }
+    if (n_tile != 64 && n_tile != 128 && n_tile != 192 && n_tile != 256) { *why = "tcgen05 variant: N tile must be 64, 128, 192 or 256"; return cudaErrorInvalidValue; }
     EncodeTiledFn enc = get_encode_tiled();
     if (!enc) { *why = "cuTensorMapEncodeTiled is not available from this driver"; return cudaErrorNotSupported; }
     const uint64_t Kg = (uint64_t)CB * CT;
@@ -472,6 +552,11 @@ cudaError_t launch_umma(const LutArgs& a, const CUtensorMap& lut_t_map, const Um
     *why = nullptr;
     if (a.M == 0 || a.N == 0) return cudaSuccess;
     if (reinterpret_cast<uintptr_t>(a.idx) & 15u) { *why = "tcgen05 variant: the index buffer must be 16-byte aligned"; return cudaErrorInvalidValue; }
+    const bool a_tmem = plan.a_tmem != 0;
+    if (!tile_ok(plan.n_tile, a_tmem)) {
+        *why = "tcgen05 variant: N tile must be 64, 128 or 256 (A in shared memory) or 64, 128 or 192 (A in tensor memory)";
+        return cudaErrorInvalidValue;
+    }
     UmmaParams p;
     p.a = a;
     p.slabs_total = (uint32_t)(((uint64_t)a.CB * a.CT + kSlabK - 1) / kSlabK);
@@ -480,10 +565,12 @@ cudaError_t launch_umma(const LutArgs& a, const CUtensorMap& lut_t_map, const Um
     p.slabs_per_item = (p.slabs_total + split - 1) / split;
     split = (p.slabs_total + p.slabs_per_item - 1) / p.slabs_per_item;  // no empty slices
     p.split = split;
-    p.stages = plan.stages ? plan.stages : default_stages(plan.n_tile);
-    if (p.stages > kMaxStages) p.stages = kMaxStages;
+    const uint32_t sps = plan.sps == 4 ? 4u : (plan.sps == 1 ? 1u : 2u);
+    const uint32_t st_max = max_stages(plan.n_tile, a_tmem, sps);
+    if (st_max < 2) { *why = "tcgen05 variant: this tile / slabs-per-stage combination leaves room for fewer than two stages"; return cudaErrorInvalidValue; }
+    p.stages = plan.stages ? plan.stages : (st_max > 4 ? 4u : st_max);
+    if (p.stages > st_max) p.stages = st_max;
     if (p.stages < 2) p.stages = 2;
-    while (p.stages > 2 && umma_smem_bytes(plan.n_tile, p.stages) > kSmemLimit) --p.stages;
     p.tiles_m = (a.M + kMTile - 1) / kMTile;
     p.tiles_n = (a.N + plan.n_tile - 1) / plan.n_tile;
     p.log2_ct = 0;
@@ -491,17 +578,31 @@ cudaError_t launch_umma(const LutArgs& a, const CUtensorMap& lut_t_map, const Um
     p.acc_scratch = acc_scratch;
     p.tile_counters = tile_counters;
     p.dev_err = dev_err;
+    // A builder group may run at most one use of a stage ahead of the MMA warp (mbarrier
+    // parity only tells two consecutive phases apart), which holds iff groups <= stages * slabs per stage.
+    p.groups = plan.groups ? (plan.groups > kMaxAgenGroups ? kMaxAgenGroups : plan.groups) : 4;
+    if (p.groups > p.stages * sps) p.groups = p.stages * sps;
     if (split > 1 && (!acc_scratch || !tile_counters)) { *why = "tcgen05 variant: split > 1 needs scratch"; return cudaErrorInvalidValue; }
-    const size_t smem = umma_smem_bytes(plan.n_tile, p.stages);
+    const size_t smem = umma_smem_bytes(plan.n_tile, p.stages, a_tmem, sps);
     const uint64_t items = (uint64_t)p.tiles_m * p.tiles_n * split;
     const uint32_t cap = plan.max_ctas ? plan.max_ctas : 148u;
     const uint32_t grid = (uint32_t)(items < cap ? items : cap);
-    switch (plan.n_tile) {
-        case 64: return run<64>(lut_t_map, p, grid, smem, s);
-        case 128: return run<128>(lut_t_map, p, grid, smem, s);
-        case 256: return run<256>(lut_t_map, p, grid, smem, s);
-        default: *why = "tcgen05 variant: N tile must be 64, 128 or 256"; return cudaErrorInvalidValue;
-    }
+#define LUTAMM_UMMA_CASE(NT, TM, SP) \
+    if (plan.n_tile == NT && a_tmem == TM && sps == SP) return run<NT, TM, SP>(lut_t_map, p, grid, smem, s);
+    LUTAMM_UMMA_CASE(64, true, 2)
+    LUTAMM_UMMA_CASE(128, true, 2)
+    LUTAMM_UMMA_CASE(192, true, 2)
+    LUTAMM_UMMA_CASE(128, true, 4)
+    LUTAMM_UMMA_CASE(64, true, 4)
+    LUTAMM_UMMA_CASE(192, true, 1)
+    LUTAMM_UMMA_CASE(64, false, 2)
+    LUTAMM_UMMA_CASE(128, false, 2)
+    LUTAMM_UMMA_CASE(256, false, 2)
+    LUTAMM_UMMA_CASE(256, false, 1)
+    LUTAMM_UMMA_CASE(128, false, 4)
+#undef LUTAMM_UMMA_CASE
+    *why = "tcgen05 variant: this tile / operand / slabs-per-stage combination is not built";
+    return cudaErrorInvalidValue;
 }
 
 // ---------------------------------------------------------------- LUT [rows][cols] -> [cols][rows]

@@ -34,8 +34,8 @@ EncodeTiledFn get_encode_tiled() {
 
 namespace {
 
-constexpr int kNumUmmaTiles = 3;  // 64, 128, 256
-inline int umma_tile_slot(uint32_t n_tile) { return n_tile == 64 ? 0 : n_tile == 128 ? 1 : 2; }
+constexpr int kNumUmmaTiles = 4;  // 64, 128, 192, 256
+inline int umma_tile_slot(uint32_t n_tile) { return n_tile == 64 ? 0 : n_tile == 128 ? 1 : n_tile == 192 ? 2 : 3; }
 
 struct Layer {
     lutamm_index_params ip{};
@@ -49,7 +49,7 @@ struct Layer {
     std::vector<CUtensorMap> gather_maps;
     std::vector<char> gather_map_ok;
     CUtensorMap umma_maps[kNumUmmaTiles];
-    bool umma_map_ok[kNumUmmaTiles] = {false, false, false};
+    bool umma_map_ok[kNumUmmaTiles] = {false, false, false, false};
 };
 
 struct Buf {
@@ -192,17 +192,21 @@ int run_lut(lutamm_ctx* c, Layer& L, const uint8_t* d_idx, float* d_out, int32_t
     if (variant == LUTAMM_VARIANT_UMMA) {
         if (!umma_supported(L.CB, L.CT, L.N))
             return fail(c, LUTAMM_EUNSUPPORTED, "tcgen05 variant does not cover this shape (num_centroid a power of two in 8..256, num_codebook % 16 == 0)");
+        // where the one-hot operand lives: tensor memory unless the plan says otherwise
+        const bool a_tmem = plan.umma_operand != 1;
         UmmaPlan up;
-        umma_default_plan(M, L.CB, L.CT, L.N, c->sm_count, &up);
+        umma_default_plan(M, L.CB, L.CT, L.N, c->sm_count, a_tmem, &up);
         if (plan.umma_n_tile) {
             up.n_tile = plan.umma_n_tile;
             up.split = umma_auto_split(M, L.CB, L.CT, L.N, up.n_tile, c->sm_count);
-            up.stages = 0;  // largest pipeline that fits
         }
         if (plan.umma_split) up.split = plan.umma_split;
-        if (plan.umma_stages) up.stages = plan.umma_stages;
-        if (up.n_tile != 64 && up.n_tile != 128 && up.n_tile != 256)
-            return fail(c, LUTAMM_EINVAL, "umma_n_tile must be 64, 128 or 256");
+        up.stages = plan.umma_stages;
+        up.groups = plan.umma_groups & 255u;
+        up.sps = plan.umma_groups >> 8;  // experimental: slabs per stage in the high bits
+        if (!umma_tile_ok(up.n_tile, a_tmem))
+            return fail(c, LUTAMM_EINVAL, "umma_n_tile must be 64, 128 or 256 with the one-hot operand in shared memory, "
+                                          "64, 128 or 192 with it in tensor memory");
         if (!L.d_lut_t) {
             const size_t bytes = (size_t)L.CB * L.CT * L.N;
             CU_TRY(c, cudaMalloc(&L.d_lut_t, bytes));
@@ -217,7 +221,7 @@ int run_lut(lutamm_ctx* c, Layer& L, const uint8_t* d_idx, float* d_out, int32_t
         }
         if (up.split > 1) {
             const uint32_t tiles = ((M + 127) / 128) * ((L.N + up.n_tile - 1) / up.n_tile);
-            int r = ensure(c, c->d_acc_scratch, (size_t)M * L.N * sizeof(int32_t), true);
+            int r = ensure(c, c->d_acc_scratch, (size_t)up.split * M * L.N * sizeof(int32_t), false);
             if (r) return r;
             r = ensure(c, c->d_counters, (size_t)tiles * sizeof(uint32_t), true);
             if (r) return r;
@@ -545,8 +549,10 @@ int lutamm_set_plan(lutamm_ctx* c, int layer_id, const lutamm_plan* plan) {
     if (!plan) return fail(c, LUTAMM_EINVAL, "null plan");
     if (plan->variant > LUTAMM_VARIANT_UMMA) return fail(c, LUTAMM_EINVAL, "unknown kernel variant");
     if (plan->gather_cfg >= gather_num_cfgs()) return fail(c, LUTAMM_EINVAL, "unknown gather tile configuration");
-    if (plan->umma_n_tile && plan->umma_n_tile != 64 && plan->umma_n_tile != 128 && plan->umma_n_tile != 256)
-        return fail(c, LUTAMM_EINVAL, "umma_n_tile must be 0, 64, 128 or 256");
+    if (plan->umma_operand > 2) return fail(c, LUTAMM_EINVAL, "umma_operand must be 0, 1 (shared memory) or 2 (tensor memory)");
+    if (plan->umma_n_tile && !umma_tile_ok(plan->umma_n_tile, plan->umma_operand != 1))
+        return fail(c, LUTAMM_EINVAL, "umma_n_tile must be 0, 64, 128 or 256 with the one-hot operand in shared memory, "
+                                      "0, 64, 128 or 192 with it in tensor memory");
     if (plan->variant == LUTAMM_VARIANT_UMMA && !umma_supported(L->CB, L->CT, L->N))
         return fail(c, LUTAMM_EUNSUPPORTED, "tcgen05 variant does not cover this shape");
     L->plan = *plan;
@@ -584,19 +590,22 @@ int lutamm_tune(lutamm_ctx* c, int layer_id, uint32_t M, lutamm_plan* best_out) 
     }
     if (umma_supported(L->CB, L->CT, L->N)) {
         const uint32_t slabs = (uint32_t)(((uint64_t)L->CB * L->CT + 127) / 128);
-        for (uint32_t nt : {128u, 256u}) {
-            if (nt > 128 && L->N < 256) continue;
-            const uint32_t tiles = ((M + 127) / 128) * ((L->N + nt - 1) / nt);
-            std::vector<uint32_t> splits = {1};
-            uint32_t s_fill = tiles < (uint32_t)c->sm_count ? (uint32_t)c->sm_count / tiles : 1;
-            for (uint32_t s : {s_fill, s_fill * 2, s_fill / 2})
-                if (s > 1 && s <= slabs / 2 && s <= 32) splits.push_back(s);
-            for (uint32_t s : splits) {
-                lutamm_plan p{};
-                p.variant = LUTAMM_VARIANT_UMMA;
-                p.umma_n_tile = nt;
-                p.umma_split = s;
-                cands.push_back(p);
+        for (uint32_t operand : {2u, 1u}) {
+            for (uint32_t nt : {128u, operand == 2u ? 192u : 256u}) {
+                if (nt > 128 && L->N < nt) continue;
+                const uint32_t tiles = ((M + 127) / 128) * ((L->N + nt - 1) / nt);
+                std::vector<uint32_t> splits = {1};
+                uint32_t s_fill = tiles < (uint32_t)c->sm_count ? (uint32_t)c->sm_count / tiles : 1;
+                for (uint32_t s : {s_fill, s_fill * 2, s_fill / 2})
+                    if (s > 1 && s <= slabs / 2 && s <= 32) splits.push_back(s);
+                for (uint32_t s : splits) {
+                    lutamm_plan p{};
+                    p.variant = LUTAMM_VARIANT_UMMA;
+                    p.umma_n_tile = nt;
+                    p.umma_split = s;
+                    p.umma_operand = operand;
+                    cands.push_back(p);
+                }
             }
         }
     }

@@ -18,11 +18,14 @@ RTOL = 1e-5  # the tolerance the task states for dequantised fp32 outputs
 def variants_for(CT, N, CB=16):
     v = [("gather", dict(variant=P.VARIANT_GATHER, gather_cfg=c)) for c in range(5)]
     if CT in (8, 16, 32, 64, 128, 256) and N % 16 == 0 and CB % 16 == 0:
-        v += [("umma128", dict(variant=P.VARIANT_UMMA, umma_n_tile=128, umma_split=1)),
-              ("umma256", dict(variant=P.VARIANT_UMMA, umma_n_tile=256, umma_split=1)),
-              ("umma64s", dict(variant=P.VARIANT_UMMA, umma_n_tile=64, umma_split=2)),
-              ("umma128s", dict(variant=P.VARIANT_UMMA, umma_n_tile=128, umma_split=3)),
-              ("umma_auto", dict(variant=P.VARIANT_UMMA))]
+        U = P.VARIANT_UMMA
+        v += [("umma_ss128", dict(variant=U, umma_operand=1, umma_n_tile=128, umma_split=1)),
+              ("umma_ss256", dict(variant=U, umma_operand=1, umma_n_tile=256, umma_split=1)),
+              ("umma_ss64s", dict(variant=U, umma_operand=1, umma_n_tile=64, umma_split=2)),
+              ("umma_ts192", dict(variant=U, umma_operand=2, umma_n_tile=192, umma_split=1)),
+              ("umma_ts128s", dict(variant=U, umma_operand=2, umma_n_tile=128, umma_split=3)),
+              ("umma_ts64", dict(variant=U, umma_operand=2, umma_n_tile=64, umma_split=1, umma_groups=2)),
+              ("umma_auto", dict(variant=U))]
     return v
 
 
@@ -131,7 +134,7 @@ def test_reference_tiled_layouts(ctx):
     want = np.zeros(M * N, dtype=np.float32)
     want[offs.ravel()] = out.ravel()
     for plan in (dict(variant=P.VARIANT_GATHER), dict(variant=P.VARIANT_UMMA, umma_split=1),
-                 dict(variant=P.VARIANT_UMMA, umma_n_tile=128, umma_split=2)):
+                 dict(variant=P.VARIANT_UMMA, umma_n_tile=128, umma_split=2), dict(variant=P.VARIANT_UMMA, umma_operand=1)):
         ctx.set_plan(5, **plan)
         y = np.zeros(M * N, dtype=np.float32)
         ctx.amm_host(5, c.x, y, n_tokens=M, flags=P.FLAG_OUTPUT_TILED)
