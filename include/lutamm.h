@@ -99,6 +99,9 @@ typedef struct lutamm_plan {
     uint32_t umma_groups;     /* tcgen05 one-hot builder groups of 4 warps (0 = default)  */
     uint32_t umma_operand;    /* where the one-hot operand lives: 0 = default,
                                  1 = shared memory, 2 = tensor memory (TMEM)             */
+    uint32_t umma_sps;        /* tcgen05: 128-byte slabs of the codebook axis per pipeline
+                                 stage, 1, 2 or 4 (0 = default)                           */
+    uint32_t reserved;
 } lutamm_plan;
 
 /* Device times of the last timed call, milliseconds (CUDA events on the context's stream).

@@ -60,11 +60,12 @@ class LUTParams(ctypes.Structure):
 class Plan(ctypes.Structure):
     _fields_ = [("variant", ctypes.c_uint32), ("ccs_tokens", ctypes.c_uint32), ("gather_cfg", ctypes.c_uint32),
                 ("umma_n_tile", ctypes.c_uint32), ("umma_split", ctypes.c_uint32), ("umma_stages", ctypes.c_uint32),
-                ("umma_groups", ctypes.c_uint32), ("umma_operand", ctypes.c_uint32)]
+                ("umma_groups", ctypes.c_uint32), ("umma_operand", ctypes.c_uint32),
+                ("umma_sps", ctypes.c_uint32), ("reserved", ctypes.c_uint32)]
 
     def as_dict(self):
         return {k: getattr(self, k) for k in ("variant", "ccs_tokens", "gather_cfg", "umma_n_tile", "umma_split",
-                                              "umma_stages", "umma_groups", "umma_operand")}
+                                              "umma_stages", "umma_groups", "umma_operand", "umma_sps")}
 
 
 class Timings(ctypes.Structure):

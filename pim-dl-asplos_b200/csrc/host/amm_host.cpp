@@ -1,0 +1,68 @@
+#include "amm_host.h"
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+namespace {
+
+struct Key {
+    lutamm_ctx* ctx;
+    const void* centroid;
+    const void* lut;
+    const void* bias;
+    bool operator<(const Key& o) const {
+        return std::tie(ctx, centroid, lut, bias) < std::tie(o.ctx, o.centroid, o.lut, o.bias);
+    }
+};
+
+std::mutex g_mu;
+std::map<Key, int> g_layers;           // weights already resident -> layer id
+std::map<lutamm_ctx*, int> g_next_id;  // ids handed out by amm_host() start high, away from user ids
+constexpr int kFirstAutoId = 1 << 20;
+
+}  // namespace
+
+int amm_host(lutamm_ctx* ctx, float* input_tensor, float* centroid_tensor, lut_data_type* lut_table,
+             float* bias_tensor, float* output_tensor, IndexCalcParams index_params, LUTParams lut_params) {
+    int id;
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        const Key k{ctx, centroid_tensor, lut_table, bias_tensor};
+        auto it = g_layers.find(k);
+        if (it == g_layers.end()) {
+            int& next = g_next_id[ctx];
+            if (next < kFirstAutoId) next = kFirstAutoId;
+            id = next++;
+            const int rc = lutamm_load_weights(ctx, id, centroid_tensor, lut_table, bias_tensor,
+                                               reinterpret_cast<const lutamm_index_params*>(&index_params),
+                                               reinterpret_cast<const lutamm_lut_params*>(&lut_params));
+            if (rc != LUTAMM_OK) return rc;
+            g_layers.emplace(k, id);
+        } else {
+            id = it->second;
+        }
+    }
+    return lutamm_amm(ctx, id, input_tensor, output_tensor, index_params.n, 0);
+}
+
+int index_calculation(lutamm_ctx* ctx, int layer_id, float* input_tensor, uint8_t* lut_input_index, uint32_t n) {
+    return lutamm_index_calculation(ctx, layer_id, input_tensor, lut_input_index, n, LUTAMM_INDEX_U8_ROWMAJOR);
+}
+
+int pim_lut(lutamm_ctx* ctx, int layer_id, uint8_t* input_index, float* output_tensor, uint32_t n) {
+    return lutamm_pim_lut(ctx, layer_id, input_index, output_tensor, n, 0);
+}
+
+void amm_host_forget(lutamm_ctx* ctx) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    for (auto it = g_layers.begin(); it != g_layers.end();) {
+        if (it->first.ctx == ctx) {
+            lutamm_unload_weights(ctx, it->second);
+            it = g_layers.erase(it);
+        } else {
+            ++it;
+        }
+    }
+    g_next_id.erase(ctx);
+}

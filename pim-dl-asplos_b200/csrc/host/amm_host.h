@@ -1,0 +1,25 @@
+// The AMM operator with the reference's own argument list
+// (inference-engine/src/host/amm_host.h:8-10), a lutamm context standing where the
+// dpu_set_t* stood, so callers written like transformer_layer.cpp keep their shape:
+//
+//     amm_host(ctx, input, centroid, lut, bias, output, index_params, lut_params);
+//
+// The reference pushes the whole LUT to the DPUs on every call (pim_lut_host.cpp:143).
+// Here the weights named by (centroid, lut, bias) are uploaded the first time they are seen
+// and stay resident; later calls with the same pointers only run the kernels.  Pointers may
+// be host or device addresses.  Returns 0 or a negative LUTAMM_E* code (the reference
+// returns void and aborts on error).
+#pragma once
+#include "defines.h"
+
+int amm_host(lutamm_ctx* ctx, float* input_tensor, float* centroid_tensor, lut_data_type* lut_table,
+             float* bias_tensor, float* output_tensor, IndexCalcParams index_params, LUTParams lut_params);
+
+// The two halves, as in index_calc_host.h:5 and pim_lut_host.h:14-15.  `layer_id` names
+// weights loaded with lutamm_load_weights(); the index buffer is uint8 [n][num_codebook].
+int index_calculation(lutamm_ctx* ctx, int layer_id, float* input_tensor, uint8_t* lut_input_index, uint32_t n);
+int pim_lut(lutamm_ctx* ctx, int layer_id, uint8_t* input_index, float* output_tensor, uint32_t n);
+
+// Forget the pointer -> layer association kept by amm_host() for this context (frees the
+// device copies).  Call before the weight buffers are reused for other contents.
+void amm_host_forget(lutamm_ctx* ctx);

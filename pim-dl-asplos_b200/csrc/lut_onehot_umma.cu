@@ -507,7 +507,7 @@ uint32_t umma_auto_split(uint32_t M, uint32_t CB, uint32_t CT, uint32_t N, uint3
     uint32_t split = 1;
     if (tiles < (uint32_t)sm_count) {
         split = (uint32_t)sm_count / tiles;
-        const uint32_t max_split = slabs / 8 ? slabs / 8 : 1;  // keep at least 8 slabs per item
+        const uint32_t max_split = slabs / 16 ? slabs / 16 : 1;  // keep at least 16 slabs per item
         if (split > max_split) split = max_split;
         if (split > 16) split = 16;
         if (split < 1) split = 1;
@@ -515,16 +515,36 @@ uint32_t umma_auto_split(uint32_t M, uint32_t CB, uint32_t CT, uint32_t N, uint3
     return split;
 }
 
-void umma_default_plan(uint32_t M, uint32_t CB, uint32_t CT, uint32_t N, int sm_count, bool a_tmem, UmmaPlan* p) {
-    uint32_t n_tile;
-    if (a_tmem) n_tile = N >= 192 ? 192 : (N > 64 ? 128 : 64);
-    else n_tile = N >= 256 ? 256 : (N > 64 ? 128 : 64);
+// Shape heuristics behind LUTAMM_VARIANT_AUTO (the tuner replaces them by measurement):
+//  * plenty of tiles and a long codebook axis: A in shared memory, 256-wide tiles - each
+//    one-hot slab then feeds the most multiply-adds, and building slabs is what binds;
+//  * plenty of tiles otherwise: A in tensor memory, 192-wide tiles (less wave quantisation,
+//    cheaper epilogue per item);
+//  * fewer tiles than SMs: 128-wide tiles, four slabs per stage, and the codebook axis
+//    split across CTAs until the SMs are covered.
+// operand / n_tile / sps != 0 force that choice.
+void umma_default_plan(uint32_t M, uint32_t CB, uint32_t CT, uint32_t N, int sm_count, uint32_t operand,
+                       uint32_t n_tile, uint32_t sps, UmmaPlan* p) {
+    const uint32_t tm = (M + kMTile - 1) / kMTile;
+    const uint32_t slabs = (uint32_t)(((uint64_t)CB * CT + kSlabK - 1) / kSlabK);
+    auto tiles_for = [&](uint32_t nt) { return tm * ((N + nt - 1) / nt); };
+    bool a_tmem;
+    if (operand == 0 && n_tile == 0) {
+        if (N >= 256 && slabs >= 128 && tiles_for(256) >= 2u * (uint32_t)sm_count) { a_tmem = false; n_tile = 256; }
+        else if (N >= 192 && tiles_for(192) >= (uint32_t)sm_count) { a_tmem = true; n_tile = 192; }
+        else { a_tmem = true; n_tile = N > 64 ? 128 : 64; if (!sps) sps = 4; }
+    } else if (operand == 0) {
+        a_tmem = n_tile != 256;
+    } else {
+        a_tmem = operand == 2;
+        if (n_tile == 0) n_tile = a_tmem ? (N >= 192 ? 192 : (N > 64 ? 128 : 64)) : (N >= 256 ? 256 : (N > 64 ? 128 : 64));
+    }
     p->n_tile = n_tile;
     p->a_tmem = a_tmem ? 1u : 0u;
     p->split = umma_auto_split(M, CB, CT, N, n_tile, sm_count);
     p->stages = 0;
     p->groups = 0;
-    p->sps = 0;
+    p->sps = sps ? sps : 2;
     p->max_ctas = (uint32_t)sm_count;
 }
 

@@ -192,18 +192,13 @@ int run_lut(lutamm_ctx* c, Layer& L, const uint8_t* d_idx, float* d_out, int32_t
     if (variant == LUTAMM_VARIANT_UMMA) {
         if (!umma_supported(L.CB, L.CT, L.N))
             return fail(c, LUTAMM_EUNSUPPORTED, "tcgen05 variant does not cover this shape (num_centroid a power of two in 8..256, num_codebook % 16 == 0)");
-        // where the one-hot operand lives: tensor memory unless the plan says otherwise
-        const bool a_tmem = plan.umma_operand != 1;
         UmmaPlan up;
-        umma_default_plan(M, L.CB, L.CT, L.N, c->sm_count, a_tmem, &up);
-        if (plan.umma_n_tile) {
-            up.n_tile = plan.umma_n_tile;
-            up.split = umma_auto_split(M, L.CB, L.CT, L.N, up.n_tile, c->sm_count);
-        }
+        umma_default_plan(M, L.CB, L.CT, L.N, c->sm_count, plan.umma_operand, plan.umma_n_tile, plan.umma_sps, &up);
+        const bool a_tmem = up.a_tmem != 0;
         if (plan.umma_split) up.split = plan.umma_split;
         up.stages = plan.umma_stages;
-        up.groups = plan.umma_groups & 255u;
-        up.sps = plan.umma_groups >> 8;  // experimental: slabs per stage in the high bits
+        up.groups = plan.umma_groups;
+        if (plan.umma_sps) up.sps = plan.umma_sps;
         if (!umma_tile_ok(up.n_tile, a_tmem))
             return fail(c, LUTAMM_EINVAL, "umma_n_tile must be 64, 128 or 256 with the one-hot operand in shared memory, "
                                           "64, 128 or 192 with it in tensor memory");
@@ -550,9 +545,11 @@ int lutamm_set_plan(lutamm_ctx* c, int layer_id, const lutamm_plan* plan) {
     if (plan->variant > LUTAMM_VARIANT_UMMA) return fail(c, LUTAMM_EINVAL, "unknown kernel variant");
     if (plan->gather_cfg >= gather_num_cfgs()) return fail(c, LUTAMM_EINVAL, "unknown gather tile configuration");
     if (plan->umma_operand > 2) return fail(c, LUTAMM_EINVAL, "umma_operand must be 0, 1 (shared memory) or 2 (tensor memory)");
-    if (plan->umma_n_tile && !umma_tile_ok(plan->umma_n_tile, plan->umma_operand != 1))
+    if (plan->umma_n_tile && plan->umma_operand && !umma_tile_ok(plan->umma_n_tile, plan->umma_operand == 2))
         return fail(c, LUTAMM_EINVAL, "umma_n_tile must be 0, 64, 128 or 256 with the one-hot operand in shared memory, "
                                       "0, 64, 128 or 192 with it in tensor memory");
+    if (plan->umma_sps != 0 && plan->umma_sps != 1 && plan->umma_sps != 2 && plan->umma_sps != 4)
+        return fail(c, LUTAMM_EINVAL, "umma_sps must be 0, 1, 2 or 4");
     if (plan->variant == LUTAMM_VARIANT_UMMA && !umma_supported(L->CB, L->CT, L->N))
         return fail(c, LUTAMM_EUNSUPPORTED, "tcgen05 variant does not cover this shape");
     L->plan = *plan;
@@ -590,22 +587,22 @@ int lutamm_tune(lutamm_ctx* c, int layer_id, uint32_t M, lutamm_plan* best_out) 
     }
     if (umma_supported(L->CB, L->CT, L->N)) {
         const uint32_t slabs = (uint32_t)(((uint64_t)L->CB * L->CT + 127) / 128);
-        for (uint32_t operand : {2u, 1u}) {
-            for (uint32_t nt : {128u, operand == 2u ? 192u : 256u}) {
-                if (nt > 128 && L->N < nt) continue;
-                const uint32_t tiles = ((M + 127) / 128) * ((L->N + nt - 1) / nt);
-                std::vector<uint32_t> splits = {1};
-                uint32_t s_fill = tiles < (uint32_t)c->sm_count ? (uint32_t)c->sm_count / tiles : 1;
-                for (uint32_t s : {s_fill, s_fill * 2, s_fill / 2})
-                    if (s > 1 && s <= slabs / 2 && s <= 32) splits.push_back(s);
-                for (uint32_t s : splits) {
-                    lutamm_plan p{};
-                    p.variant = LUTAMM_VARIANT_UMMA;
-                    p.umma_n_tile = nt;
-                    p.umma_split = s;
-                    p.umma_operand = operand;
-                    cands.push_back(p);
-                }
+        struct Cand { uint32_t operand, n_tile, sps; };
+        for (const Cand& cd : {Cand{1, 256, 2}, Cand{2, 192, 2}, Cand{2, 128, 4}, Cand{2, 128, 2}, Cand{1, 128, 2}}) {
+            if (cd.n_tile > 128 && L->N < cd.n_tile) continue;
+            const uint32_t tiles = ((M + 127) / 128) * ((L->N + cd.n_tile - 1) / cd.n_tile);
+            std::vector<uint32_t> splits = {1};
+            uint32_t s_fill = tiles < (uint32_t)c->sm_count ? (uint32_t)c->sm_count / tiles : 1;
+            for (uint32_t s : {s_fill, s_fill * 2, s_fill / 2})
+                if (s > 1 && s <= slabs / 4 && s <= 32) splits.push_back(s);
+            for (uint32_t s : splits) {
+                lutamm_plan p{};
+                p.variant = LUTAMM_VARIANT_UMMA;
+                p.umma_n_tile = cd.n_tile;
+                p.umma_split = s;
+                p.umma_operand = cd.operand;
+                p.umma_sps = cd.sps;
+                cands.push_back(p);
             }
         }
     }
