@@ -83,7 +83,11 @@ ccs_reg_kernel(const float* __restrict__ x, const float* __restrict__ cent, void
 #pragma unroll
     for (int t = 0; t < kTok; ++t) load_x<V>(xp + (size_t)min(m0 + t, M - 1) * K, xs[t]);
 
-    float c[CT][V];
+    // Centroids are kept negated so that x - c becomes x + (-c): the same IEEE result, and
+    // for even V two dimensions go through one packed add.rn.f32x2 / mul.rn.f32x2 (each lane
+    // of a packed operation rounds on its own, and add and mul stay separate instructions,
+    // so this is still the reference's unfused arithmetic).
+    float nc[CT][V];
     {
         const float* cp = cent + (size_t)cb * CT * V;
 #pragma unroll
@@ -91,7 +95,7 @@ ccs_reg_kernel(const float* __restrict__ x, const float* __restrict__ cent, void
             float t[V];
             load_x<V>(cp + ct * V, t);
 #pragma unroll
-            for (int d = 0; d < V; ++d) c[ct][d] = t[d];
+            for (int d = 0; d < V; ++d) nc[ct][d] = -t[d];
         }
     }
 
@@ -112,10 +116,20 @@ ccs_reg_kernel(const float* __restrict__ x, const float* __restrict__ cent, void
 #pragma unroll
             for (int t = 0; t < kTok; ++t) {
                 float acc = 0.f;
+                if constexpr (V % 2 == 0) {
 #pragma unroll
-                for (int d = 0; d < V; ++d) {
-                    float e = __fsub_rn(cur[t][d], c[ct][d]);
-                    acc = __fadd_rn(acc, __fmul_rn(e, e));
+                    for (int d = 0; d < V; d += 2) {
+                        const float2 e = __fadd2_rn(make_float2(cur[t][d], cur[t][d + 1]), make_float2(nc[ct][d], nc[ct][d + 1]));
+                        const float2 sq = __fmul2_rn(e, e);
+                        acc = (d == 0) ? sq.x : __fadd_rn(acc, sq.x);  // 0 + sq.x is exact
+                        acc = __fadd_rn(acc, sq.y);
+                    }
+                } else {
+#pragma unroll
+                    for (int d = 0; d < V; ++d) {
+                        const float e = __fadd_rn(cur[t][d], nc[ct][d]);
+                        acc = __fadd_rn(acc, __fmul_rn(e, e));
+                    }
                 }
                 if (ct == 0) {
                     mn[t] = acc;
