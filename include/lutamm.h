@@ -190,6 +190,32 @@ int lutamm_get_timings(lutamm_ctx* ctx, lutamm_timings* out);
 /* Kernels of this library launched on this context since creation. */
 uint64_t lutamm_launch_count(const lutamm_ctx* ctx);
 
+/* ---- for callers that must not allocate -------------------------------------------- */
+
+/* Device bytes of index scratch compiled into the library for lutamm_amm_static_scratch();
+ * every GPU that loads the library holds them (plus 256) until the process exits. */
+#define LUTAMM_STATIC_SCRATCH_BYTES (8u * 1024u * 1024u)
+
+/* The whole AMM (search + gather-accumulate + dequantise, CUDA-core gather variant) without
+ * any allocation: no cudaMalloc/cudaFree, no pooled allocator, no context.  It has no
+ * counterpart in the reference.  It is for hosts that fix their device-memory layout at
+ * start-up and forbid allocation afterwards (serving processes with pre-sized arenas,
+ * latency-critical loops, plug-in hosts that pass a fixed set of buffers).
+ * All five buffers are DEVICE memory of `device`, laid out as for lutamm_load_weights /
+ * lutamm_amm; n_tokens = index_params->n.  The index buffer between the two kernels lives in
+ * a fixed __device__ array: n * num_codebook > LUTAMM_STATIC_SCRATCH_BYTES is rejected with
+ * LUTAMM_EINVAL.  The call is synchronous on `cuda_stream` (a cudaStream_t, NULL = default
+ * stream).  All calls in a process share the array on a device, so calls that overlap on the
+ * GPU race: serialise them.  The first call on a device resolves the array's device address
+ * (cudaGetSymbolAddress) and should therefore come before any stream capture.
+ * Error text: lutamm_static_scratch_last_error() (per thread). */
+int lutamm_amm_static_scratch(int device, void* cuda_stream,
+                              const float* input, const float* centroid, const int8_t* lut,
+                              const float* bias, float* output,
+                              const lutamm_index_params* index_params,
+                              const lutamm_lut_params* lut_params);
+const char* lutamm_static_scratch_last_error(void);
+
 #ifdef __cplusplus
 }
 #endif

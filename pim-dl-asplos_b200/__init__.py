@@ -28,6 +28,7 @@ ABI_SYMBOLS = [
     "lutamm_version", "lutamm_load_weights", "lutamm_unload_weights", "lutamm_amm", "lutamm_amm_debug",
     "lutamm_index_calculation", "lutamm_pim_lut", "lutamm_set_plan", "lutamm_get_plan", "lutamm_tune",
     "lutamm_enable_timing", "lutamm_get_timings", "lutamm_launch_count",
+    "lutamm_amm_static_scratch", "lutamm_static_scratch_last_error",
 ]
 
 
@@ -109,8 +110,12 @@ def load_library() -> ctypes.CDLL:
     L.lutamm_get_timings.argtypes = [vp, ctypes.POINTER(Timings)]
     L.lutamm_launch_count.argtypes = [vp]
     L.lutamm_launch_count.restype = ctypes.c_uint64
+    L.lutamm_amm_static_scratch.argtypes = [i32, vp, vp, vp, vp, vp, vp, ctypes.POINTER(IndexCalcParams),
+                                            ctypes.POINTER(LUTParams)]
+    L.lutamm_static_scratch_last_error.argtypes = []
+    L.lutamm_static_scratch_last_error.restype = ctypes.c_char_p
     for name in ABI_SYMBOLS:
-        if name not in ("lutamm_version", "lutamm_last_error", "lutamm_launch_count"):
+        if name not in ("lutamm_version", "lutamm_last_error", "lutamm_launch_count", "lutamm_static_scratch_last_error"):
             getattr(L, name).restype = i32
     _lib = L
     return L

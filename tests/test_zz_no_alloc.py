@@ -1,0 +1,72 @@
+"""GPU check of lutamm_amm_static_scratch(), the entry point for hosts that must not allocate
+device memory after start-up (pre-sized serving arenas, latency-critical loops, plug-in hosts
+with a fixed buffer set).  Its index scratch is a fixed __device__ array inside the library
+instead of the context's grow-only arena.
+
+Called through the C ABI, twice in a row with different shapes so the second call meets the
+first call's leftovers in the shared array, and compared with the regular lutamm_amm() entry
+point: same kernels, same arithmetic, so the fp32 outputs must be bit-identical (the suite's
+bar for this path; 1e-5 relative is the stated tolerance).  This file sorts last on purpose:
+a run that stops at the first failure has then already run every other test.
+"""
+import ctypes
+
+import numpy as np
+import pytest
+
+import pim_dl_asplos_b200 as P
+from pim_dl_asplos_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+
+def _run_both(lib, ctx, M, K, N, v, CT, seed, layer_id):
+    import torch
+    c = synth.make_case(M=M, K=K, N=N, v=v, CT=CT, seed=seed)
+    CB = K // v
+    dev = dict(device="cuda:0")
+    x = torch.from_numpy(c.x).to(**dev)
+    cen = torch.from_numpy(c.centroid).to(**dev)
+    lut = torch.from_numpy(c.lut).to(**dev)
+    bias = torch.from_numpy(c.bias).to(**dev)
+    y_static = torch.full((M, N), float("nan"), dtype=torch.float32, **dev)
+    y_ctx = torch.empty(M, N, dtype=torch.float32, **dev)
+    torch.cuda.synchronize()
+    ip, lp = P.make_params(M, K, N, CB, CT, c.scale, c.lut_bias)
+    rc = lib.lutamm_amm_static_scratch(0, None, x.data_ptr(), cen.data_ptr(), lut.data_ptr(), bias.data_ptr(),
+                                       y_static.data_ptr(), ctypes.byref(ip), ctypes.byref(lp))
+    assert rc == P.OK, lib.lutamm_static_scratch_last_error().decode()
+    ctx.load_weights(layer_id, cen, lut, bias, c.scale, c.lut_bias)
+    ctx.set_plan(layer_id, variant=P.VARIANT_GATHER)
+    ctx.amm_host(layer_id, x, y_ctx)
+    ctx.unload_weights(layer_id)
+    a, b = y_static.cpu().numpy(), y_ctx.cpu().numpy()
+    np.testing.assert_allclose(a, b, rtol=1e-5, atol=0)
+    assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+
+
+def test_static_scratch_entry_point_matches_the_regular_one_twice():
+    lib = P.load_library()
+    ctx = P.LutAmmContext(0)
+    try:
+        _run_both(lib, ctx, 300, 256, 512, 2, 16, seed=71, layer_id=900)   # fills 38400 index bytes
+        _run_both(lib, ctx, 77, 96, 48, 4, 8, seed=72, layer_id=901)       # smaller: leftovers stay behind it
+    finally:
+        ctx.close()
+
+
+def test_static_scratch_rejects_what_does_not_fit():
+    import torch
+    lib = P.load_library()
+    M, K, N, CB, CT = 8192, 4096, 16, 2048, 16                           # 16 Mi index bytes > 8 Mi
+    ip, lp = P.make_params(M, K, N, CB, CT, 0.01, 0.0)
+    t = torch.zeros(16, device="cuda:0")
+    rc = lib.lutamm_amm_static_scratch(0, None, t.data_ptr(), t.data_ptr(), t.data_ptr(), t.data_ptr(), t.data_ptr(),
+                                       ctypes.byref(ip), ctypes.byref(lp))
+    assert rc == P.EINVAL
+    assert b"exceed the static scratch" in lib.lutamm_static_scratch_last_error()
+    host = np.zeros(16, dtype=np.float32)
+    ip, lp = P.make_params(4, 32, 16, 16, 8, 0.01, 0.0)
+    rc = lib.lutamm_amm_static_scratch(0, None, host.ctypes.data, t.data_ptr(), t.data_ptr(), t.data_ptr(), t.data_ptr(),
+                                       ctypes.byref(ip), ctypes.byref(lp))
+    assert rc == P.EINVAL and b"device memory" in lib.lutamm_static_scratch_last_error()
