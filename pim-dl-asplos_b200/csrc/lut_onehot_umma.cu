@@ -42,11 +42,11 @@ namespace {
 constexpr uint32_t kMTile = 128;
 constexpr uint32_t kSlabK = 128;               // bytes of K per pipeline stage = one swizzle row
 constexpr uint32_t kABytes = kMTile * kSlabK;  // 16 KiB
-constexpr uint32_t kMaxAgenGroups = 6;  // each group: 4 warps = 128 rows
+constexpr uint32_t kMaxAgenGroups = 4;  // each group: 4 warps = 128 rows (more groups measured slower)
 constexpr uint32_t kEpiWarps = 4;
 constexpr uint32_t kEpiThreads = kEpiWarps * 32;
 constexpr uint32_t kFirstAgenWarp = 2;
-constexpr uint32_t kMaxThreads = (kFirstAgenWarp + 4 * kMaxAgenGroups + kEpiWarps) * 32;  // 960
+constexpr uint32_t kMaxThreads = (kFirstAgenWarp + 4 * kMaxAgenGroups + kEpiWarps) * 32;  // 704
 constexpr uint32_t kMaxStages = 8;
 constexpr uint32_t kStageWarpBytes = 32 * 128;           // epilogue transpose buffer per warp
 
@@ -67,12 +67,20 @@ struct UmmaParams {
 __device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t n) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n) : "memory");
 }
-// 16 bytes with byte `i` (0..15) set to 1; i >= 16 gives zeros.
-__device__ __forceinline__ uint4 onehot16(uint32_t i) {
-    const uint32_t bit = 1u << ((i & 3u) * 8u);
-    const uint32_t q = i >> 2;
-    return make_uint4(q == 0 ? bit : 0u, q == 1 ? bit : 0u, q == 2 ? bit : 0u, q == 3 ? bit : 0u);
+// 64-bit left shift with PTX semantics: a shift amount of 64 or more gives 0 (shl.b64 clamps).
+__device__ __forceinline__ uint64_t shl64_clamped(uint64_t v, uint32_t n) {
+    uint64_t r;
+    asm("shl.b64 %0, %1, %2;" : "=l"(r) : "l"(v), "r"(n));
+    return r;
 }
+// 16 bytes with byte `i` set to 1, given n = 8*i; any n >= 128 gives zeros.  Two clamped 64-bit
+// shifts: the low half is 1 << n (zero once n >= 64), the high half 1 << (n - 64), where the
+// unsigned wrap-around of n - 64 for n < 64 is a huge shift amount and so also gives zero.
+__device__ __forceinline__ uint4 onehot16_bits(uint32_t n) {
+    const uint64_t lo = shl64_clamped(1ull, n), hi = shl64_clamped(1ull, n - 64u);
+    return make_uint4((uint32_t)lo, (uint32_t)(lo >> 32), (uint32_t)hi, (uint32_t)(hi >> 32));
+}
+__device__ __forceinline__ uint4 onehot16(uint32_t i) { return onehot16_bits(i < 16u ? i * 8u : 128u); }
 
 struct Item {
     uint32_t m0, n0, slab_begin, nslab, tile, z;
@@ -252,9 +260,10 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
                 if (i + kAgenGroups < it.nslab) raw_next = load_raw(grow, slab + kAgenGroups);
                 uint4 chunk[8];
                 if (lg == 4) {  // one codebook == one 16-byte chunk
+                    // indices are < 16, so 8*idx still fits its byte: shift all four at once
+                    const uint32_t n8[2] = {raw.x << 3, raw.y << 3};
 #pragma unroll
-                    for (uint32_t j = 0; j < 8; ++j)
-                        chunk[j] = onehot16(((j < 4 ? raw.x : raw.y) >> (8 * (j & 3))) & 0xFFu);
+                    for (uint32_t j = 0; j < 8; ++j) chunk[j] = onehot16_bits((n8[j >> 2] >> (8 * (j & 3))) & 0xFFu);
                 } else if (lg == 3) {  // two codebooks per chunk
                     const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
@@ -318,12 +327,21 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
         for (uint32_t item = blockIdx.x; item < n_items; item += gridDim.x, ++t) {
             const Item it = decode_item(p, item, N_TILE);
             const uint32_t ab = t & 1, aph = (t >> 1) & 1;
+            // The bias values are fetched one chunk ahead, the first before the accumulator is
+            // waited for: a miss to DRAM would otherwise sit on the critical path of every chunk.
+            auto load_bias = [&](uint32_t c) -> float4 {
+                const uint32_t n = it.n0 + c * 32 + ch * 4;
+                return n < a.N ? __ldg(reinterpret_cast<const float4*>(a.bias + n)) : make_float4(0.f, 0.f, 0.f, 0.f);
+            };
+            float4 b_next = load_bias(0);
             uint32_t w_ok = 1;
             if (lane == 0) w_ok = (ok && mbar_wait(acc_full0 + 8 * ab, aph, s_abort)) ? 1u : 0u;
             ok = __shfl_sync(0xffffffffu, w_ok, 0) != 0;
             if (ok) {
                 tc_fence_after_sync();
                 for (uint32_t c = 0; c < N_TILE / 32; ++c) {
+                    const float4 b4 = b_next;
+                    if (c + 1 < N_TILE / 32) b_next = load_bias(c + 1);
                     uint32_t v[32];
                     tmem_ld_32x32b_x32(tmem_base + ((quad * 32u) << 16) + ab * N_TILE + c * 32u, v);
                     tmem_ld_wait();
@@ -340,7 +358,6 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
                     __syncwarp();
                     const uint32_t n = it.n0 + c * 32 + ch * 4;
                     if (n < a.N) {  // N % 16 == 0: a 4-column group is in or out as a whole
-                        const float4 b4 = __ldg(reinterpret_cast<const float4*>(a.bias + n));
 #pragma unroll
                         for (uint32_t pass = 0; pass < 8; ++pass) {
                             const uint32_t rr = pass * 4 + rsub;
