@@ -36,7 +36,9 @@ extern "C" {
 #define LUTAMM_ENOMEM       -6
 
 /* flags for lutamm_amm / lutamm_pim_lut */
-#define LUTAMM_FLAG_ASYNC         1u  /* do not synchronise the stream before returning (device buffers only) */
+#define LUTAMM_FLAG_ASYNC         1u  /* return without waiting; input and output both device memory, or both
+                                         host memory (pinned, for real overlap) that stays valid and untouched
+                                         until lutamm_sync() */
 #define LUTAMM_FLAG_OUTPUT_TILED  2u  /* write the output in the reference's DPU-tiled layout
                                          [dpu][f_mtile][n_in_stile][f_in_mtile] (pim_lut_kernel.c:183,
                                          test_amm.cpp:193-202) instead of row-major [M][N]          */

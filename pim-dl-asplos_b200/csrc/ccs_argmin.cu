@@ -73,13 +73,13 @@ ccs_reg_kernel(const float* __restrict__ x, const float* __restrict__ cent, void
     // waits for this grid to finish before it touches the indices.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const uint32_t cb = blockIdx.x * kRegThreads + threadIdx.x;
-    if (cb >= CB) return;
+    const bool active = cb < CB;
     const uint32_t m0 = blockIdx.y * tokens_per_cta;
     const uint32_t m1 = min(M, m0 + tokens_per_cta);
 
     // first batch of activations before the centroids, so both round trips overlap
     float xs[kTok][V];
-    const float* xp = x + (size_t)cb * V;
+    const float* xp = x + (size_t)(active ? cb : 0) * V;
 #pragma unroll
     for (int t = 0; t < kTok; ++t) load_x<V>(xp + (size_t)min(m0 + t, M - 1) * K, xs[t]);
 
@@ -87,17 +87,28 @@ ccs_reg_kernel(const float* __restrict__ x, const float* __restrict__ cent, void
     // for even V two dimensions go through one packed add.rn.f32x2 / mul.rn.f32x2 (each lane
     // of a packed operation rounds on its own, and add and mul stay separate instructions,
     // so this is still the reference's unfused arithmetic).
-    float nc[CT][V];
+    // The CTA's 128 codebooks x CT x V centroid floats are contiguous in memory: fetch them
+    // coalesced into shared memory (row pitch CT*V + 1 floats, so both the staging stores and the
+    // per-thread reads below are bank-conflict free), instead of every lane walking its own
+    // 128-byte stretch of global memory.
+    constexpr int kRow = CT * V;
+    __shared__ float s_cent[kRegThreads * (kRow + 1)];
     {
-        const float* cp = cent + (size_t)cb * CT * V;
-#pragma unroll
-        for (int ct = 0; ct < CT; ++ct) {
-            float t[V];
-            load_x<V>(cp + ct * V, t);
-#pragma unroll
-            for (int d = 0; d < V; ++d) nc[ct][d] = -t[d];
+        const uint32_t cb0 = blockIdx.x * kRegThreads;
+        const uint32_t n_cb = min((uint32_t)kRegThreads, CB - cb0);
+        const float* gp = cent + (size_t)cb0 * kRow;
+        for (uint32_t e = threadIdx.x; e < n_cb * kRow; e += kRegThreads) {
+            const uint32_t r = e / kRow, i = e % kRow;
+            s_cent[r * (kRow + 1) + i] = __ldg(gp + e);
         }
     }
+    __syncthreads();
+    if (!active) return;
+    float nc[CT][V];
+#pragma unroll
+    for (int ct = 0; ct < CT; ++ct)
+#pragma unroll
+        for (int d = 0; d < V; ++d) nc[ct][d] = -s_cent[threadIdx.x * (kRow + 1) + ct * V + d];
 
     for (uint32_t m = m0; m < m1; m += kTok) {
         float cur[kTok][V];

@@ -5,6 +5,7 @@
 #include "../../include/lutamm.h"
 #include "kernels.h"
 
+#include <algorithm>
 #include <cstdio>
 #include <cstring>
 #include <map>
@@ -66,6 +67,11 @@ struct lutamm_ctx {
     cudaStream_t stream = nullptr;
     std::map<int, Layer> layers;
     Buf d_in, d_out, d_idx, d_idx16, d_acc_dbg, d_acc_scratch, d_counters;
+    // host-buffer pipeline: copy-in and copy-out streams, two staging slots
+    cudaStream_t s_in = nullptr, s_out = nullptr;
+    Buf p_in[2], p_out[2];
+    cudaEvent_t ev_in[2] = {}, ev_comp[2] = {}, ev_out[2] = {};
+    uint32_t slot = 0;
     uint32_t* d_err = nullptr;
     uint32_t* h_err = nullptr;  // pinned
     bool timing = false;
@@ -107,7 +113,9 @@ struct DeviceGuard {
 int ensure(lutamm_ctx* c, Buf& b, size_t bytes, bool zero = false) {
     if (bytes <= b.cap) return LUTAMM_OK;
     // Stream order: everything queued so far may still use the old block.
+    if (c->s_in) CU_TRY(c, cudaStreamSynchronize(c->s_in));
     CU_TRY(c, cudaStreamSynchronize(c->stream));
+    if (c->s_out) CU_TRY(c, cudaStreamSynchronize(c->s_out));
     if (b.p) CU_TRY(c, cudaFree(b.p));
     b.p = nullptr;
     b.cap = 0;
@@ -264,14 +272,54 @@ int run_ccs(lutamm_ctx* c, Layer& L, const float* d_x, void* d_idx, uint32_t M, 
 
 // read back the device error word after a synchronisation
 int check_dev_err(lutamm_ctx* c) {
+    if (c->s_in) CU_TRY(c, cudaStreamSynchronize(c->s_in));
     CU_TRY(c, cudaMemcpyAsync(c->h_err, c->d_err, sizeof(uint32_t), cudaMemcpyDeviceToHost, c->stream));
     CU_TRY(c, cudaStreamSynchronize(c->stream));
+    if (c->s_out) CU_TRY(c, cudaStreamSynchronize(c->s_out));
     if (*c->h_err) {
         const uint32_t code = *c->h_err;
         cudaMemsetAsync(c->d_err, 0, sizeof(uint32_t), c->stream);
         return fail(c, LUTAMM_EDEVICE, "a kernel gave up on a bounded wait (code " + std::to_string(code) + "); output is not valid");
     }
     return LUTAMM_OK;
+}
+
+// Host buffers on both sides: a three-stream pipeline.  Rows go through in chunks; chunk j is
+// copied in on s_in, computed on the context's stream and copied out on s_out, each stage
+// ordered by events, with two staging slots so that the copy-in of the next chunk (or of the
+// next call, with LUTAMM_FLAG_ASYNC), the kernels and the copy-out of the previous one overlap
+// and both directions of the host link are busy at once.  The reference's counterpart are the
+// serial host<->DPU transfers around dpu_launch (pim_lut_host.cpp:143-181).
+int amm_host_pipelined(lutamm_ctx* c, Layer& L, const float* input, float* output, uint32_t M, uint32_t flags) {
+    uint32_t chunks = M >= 2048 ? M / 1024 : 1;
+    if (chunks > 4) chunks = 4;
+    uint32_t rows = ((M + chunks - 1) / chunks + 127) / 128 * 128;
+    if ((flags & LUTAMM_FLAG_OUTPUT_TILED) || rows >= M) { rows = M; }
+    int r;
+    if ((r = ensure(c, c->d_idx, (size_t)rows * L.CB))) return r;
+    for (int k = 0; k < 2; ++k) {
+        if ((r = ensure(c, c->p_in[k], (size_t)rows * L.K * sizeof(float)))) return r;
+        if ((r = ensure(c, c->p_out[k], (size_t)rows * L.N * sizeof(float)))) return r;
+    }
+    for (uint32_t m0 = 0; m0 < M; m0 += rows) {
+        const uint32_t m = std::min(rows, M - m0);
+        const uint32_t k = c->slot++ & 1u;
+        float* d_x = static_cast<float*>(c->p_in[k].p);
+        float* d_y = static_cast<float*>(c->p_out[k].p);
+        CU_TRY(c, cudaStreamWaitEvent(c->s_in, c->ev_comp[k], 0));   // kernels that read this slot are done
+        CU_TRY(c, cudaMemcpyAsync(d_x, input + (size_t)m0 * L.K, (size_t)m * L.K * sizeof(float), cudaMemcpyHostToDevice, c->s_in));
+        CU_TRY(c, cudaEventRecord(c->ev_in[k], c->s_in));
+        CU_TRY(c, cudaStreamWaitEvent(c->stream, c->ev_in[k], 0));
+        CU_TRY(c, cudaStreamWaitEvent(c->stream, c->ev_out[k], 0));  // the slot's previous result has left
+        if ((r = run_ccs(c, L, d_x, c->d_idx.p, m, LUTAMM_INDEX_U8_ROWMAJOR))) return r;
+        if ((r = run_lut(c, L, static_cast<const uint8_t*>(c->d_idx.p), d_y, nullptr, m, flags, L.plan))) return r;
+        CU_TRY(c, cudaEventRecord(c->ev_comp[k], c->stream));
+        CU_TRY(c, cudaStreamWaitEvent(c->s_out, c->ev_comp[k], 0));
+        CU_TRY(c, cudaMemcpyAsync(output + (size_t)m0 * L.N, d_y, (size_t)m * L.N * sizeof(float), cudaMemcpyDeviceToHost, c->s_out));
+        CU_TRY(c, cudaEventRecord(c->ev_out[k], c->s_out));
+    }
+    if (flags & LUTAMM_FLAG_ASYNC) return LUTAMM_OK;
+    return check_dev_err(c);
 }
 
 int amm_impl(lutamm_ctx* c, int layer_id, const float* input, float* output, uint32_t M, uint8_t* idx_out,
@@ -287,8 +335,10 @@ int amm_impl(lutamm_ctx* c, int layer_id, const float* input, float* output, uin
         if (r) return r;
     }
     const bool in_dev = is_device_ptr(input), out_dev = is_device_ptr(output);
-    if ((flags & LUTAMM_FLAG_ASYNC) && !(in_dev && out_dev && !idx_out && !acc_out))
-        return fail(c, LUTAMM_EINVAL, "LUTAMM_FLAG_ASYNC needs device input and output buffers and no debug outputs");
+    const bool both_host = !in_dev && !out_dev;
+    if ((flags & LUTAMM_FLAG_ASYNC) && !(((in_dev && out_dev) || both_host) && !idx_out && !acc_out))
+        return fail(c, LUTAMM_EINVAL, "LUTAMM_FLAG_ASYNC needs input and output both in device memory or both in host memory, and no debug outputs");
+    if (both_host && !idx_out && !acc_out && !c->timing) return amm_host_pipelined(c, *L, input, output, M, flags);
     if (in_dev && (reinterpret_cast<uintptr_t>(input) & 3u)) return fail(c, LUTAMM_EINVAL, "input is not 4-byte aligned");
     if (out_dev && (reinterpret_cast<uintptr_t>(output) & 15u)) return fail(c, LUTAMM_EINVAL, "device output must be 16-byte aligned");
 
@@ -377,6 +427,13 @@ int lutamm_create(lutamm_ctx** out, int device) {
     *c->h_err = 0;
     c->stream = c->own_stream;
     for (auto& ev : c->ev) cudaEventCreate(&ev);
+    cudaStreamCreateWithFlags(&c->s_in, cudaStreamNonBlocking);
+    cudaStreamCreateWithFlags(&c->s_out, cudaStreamNonBlocking);
+    for (int k = 0; k < 2; ++k) {
+        cudaEventCreateWithFlags(&c->ev_in[k], cudaEventDisableTiming);
+        cudaEventCreateWithFlags(&c->ev_comp[k], cudaEventDisableTiming);
+        cudaEventCreateWithFlags(&c->ev_out[k], cudaEventDisableTiming);
+    }
     *out = c;
     return LUTAMM_OK;
 }
@@ -384,8 +441,18 @@ int lutamm_create(lutamm_ctx** out, int device) {
 int lutamm_destroy(lutamm_ctx* c) {
     if (!c) return LUTAMM_OK;
     DeviceGuard g(c->device);
+    if (c->s_in) cudaStreamSynchronize(c->s_in);
     cudaStreamSynchronize(c->stream);
+    if (c->s_out) cudaStreamSynchronize(c->s_out);
     for (auto& kv : c->layers) free_layer(kv.second);
+    for (int k = 0; k < 2; ++k) {
+        cudaFree(c->p_in[k].p); cudaFree(c->p_out[k].p);
+        if (c->ev_in[k]) cudaEventDestroy(c->ev_in[k]);
+        if (c->ev_comp[k]) cudaEventDestroy(c->ev_comp[k]);
+        if (c->ev_out[k]) cudaEventDestroy(c->ev_out[k]);
+    }
+    if (c->s_in) cudaStreamDestroy(c->s_in);
+    if (c->s_out) cudaStreamDestroy(c->s_out);
     for (Buf* b : {&c->d_in, &c->d_out, &c->d_idx, &c->d_idx16, &c->d_acc_dbg, &c->d_acc_scratch, &c->d_counters})
         cudaFree(b->p);
     cudaFree(c->d_err);

@@ -224,3 +224,23 @@ def test_large_shape_properties(ctx):
     ctx.amm_host(9, xd[:8192], y2)
     assert torch.equal(y2.view(torch.int32), yd[:8192].view(torch.int32))
     ctx.unload_weights(9)
+
+
+def test_host_buffers_pipelined_and_async(ctx):
+    """Host input and output go through the three-stream chunked pipeline; queued without waiting
+    (pinned buffers) and collected by one sync they must still give the oracle's bytes."""
+    import torch
+    c = synth.make_case(M=4500, K=256, N=512, v=2, CT=16, seed=21)   # 4 chunks, the last one ragged
+    out, _, _ = oracle.amm(c.x, c.centroid, c.lut, c.bias, c.scale)
+    ctx.load_weights(11, c.centroid, c.lut, c.bias, c.scale)
+    y = np.zeros_like(out)
+    ctx.amm_host(11, c.x, y)                                          # synchronous, pageable memory
+    assert np.array_equal(y.view(np.uint32), out.view(np.uint32))
+    xp = torch.from_numpy(c.x).pin_memory()
+    ys = [torch.zeros(4500, 512).pin_memory() for _ in range(3)]
+    for yy in ys:
+        ctx.amm_host(11, xp, yy, flags=P.FLAG_ASYNC)
+    ctx.sync()
+    for yy in ys:
+        assert np.array_equal(yy.numpy().view(np.uint32), out.view(np.uint32))
+    ctx.unload_weights(11)
