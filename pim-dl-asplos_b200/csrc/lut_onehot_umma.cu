@@ -178,10 +178,14 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
         }
         __syncwarp();
     } else if (warp == 1) {
-        // ---------------- MMA issuer
-        if (lane == 0) {
+        // ---------------- MMA issuer: the whole warp walks the loop converged (waits and
+        // descriptor arithmetic stay warp-uniform), one elected lane issues.
+        {
             uint32_t s = 0, ph = 0, t = 0;
             bool ok = true;
+            const uint32_t b_lo0 = (uint32_t)umma_desc_k_sw128(smem_u32(s_b));
+            const uint32_t a_lo0 = (uint32_t)umma_desc_k_sw128(smem_u32(s_a));
+            const uint32_t desc_hi = (uint32_t)(umma_desc_k_sw128(0) >> 32);
             for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++t) {
                 const Item it = decode_item(p, item, N_TILE);
                 const uint32_t rounds = (it.nslab + SPS - 1) / SPS;
@@ -195,27 +199,34 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
                     if (!ok) break;
                     tc_fence_after_sync();
                     const uint32_t valid = min(SPS, it.nslab - rr * SPS);
+                    if (elect_one()) {
 #pragma unroll
-                    for (uint32_t h = 0; h < SPS; ++h) {
-                        if (h < valid) {
-                            const uint64_t db = umma_desc_k_sw128(smem_u32(s_b + (size_t)(s * SPS + h) * kBBytes));
-                            if constexpr (A_TMEM) {
-                                const uint32_t ta = tmem_base + kATmemBase + (s * SPS + h) * 32;
+                        for (uint32_t h = 0; h < SPS; ++h) {
+                            if (h < valid) {
+                                // descriptors differ from the first slab's only in the 16-byte-unit address field
+                                const uint32_t b_lo = b_lo0 + (s * SPS + h) * (kBBytes >> 4);
+                                if constexpr (A_TMEM) {
+                                    const uint32_t ta = tmem_base + kATmemBase + (s * SPS + h) * 32;
 #pragma unroll
-                                for (uint32_t kk = 0; kk < kSlabK / 32; ++kk)  // 32 bytes of K = 8 TMEM columns of A
-                                    umma_i8_ts(d_tmem, ta + 8 * kk, db + 2 * kk, kIdesc, (rr | h | kk) != 0 ? 1u : 0u);
-                            } else {
-                                const uint64_t da = umma_desc_k_sw128(smem_u32(s_a + (size_t)(s * SPS + h) * kABytes));
+                                    for (uint32_t kk = 0; kk < kSlabK / 32; ++kk)  // 32 bytes of K = 8 TMEM columns of A
+                                        umma_i8_ts(d_tmem, ta + 8 * kk, ((uint64_t)desc_hi << 32) | (b_lo + 2 * kk), kIdesc,
+                                                   (rr | h | kk) != 0 ? 1u : 0u);
+                                } else {
+                                    const uint32_t a_lo = a_lo0 + (s * SPS + h) * (kABytes >> 4);
 #pragma unroll
-                                for (uint32_t kk = 0; kk < kSlabK / 32; ++kk)  // 32 bytes of K per instruction
-                                    umma_i8(d_tmem, da + 2 * kk, db + 2 * kk, kIdesc, (rr | h | kk) != 0 ? 1u : 0u);
+                                    for (uint32_t kk = 0; kk < kSlabK / 32; ++kk)  // 32 bytes of K per instruction
+                                        umma_i8(d_tmem, ((uint64_t)desc_hi << 32) | (a_lo + 2 * kk),
+                                                ((uint64_t)desc_hi << 32) | (b_lo + 2 * kk), kIdesc, (rr | h | kk) != 0 ? 1u : 0u);
+                                }
                             }
                         }
+                        umma_commit(empty0 + 8 * s);  // frees the stage once these MMAs have read it
                     }
-                    umma_commit(empty0 + 8 * s);  // frees the stage once these MMAs have read it
+                    __syncwarp();
                     if (++s == S) { s = 0; ph ^= 1; }
                 }
-                if (ok) umma_commit(acc_full0 + 8 * ab);
+                if (ok && elect_one()) umma_commit(acc_full0 + 8 * ab);
+                __syncwarp();
             }
         }
         __syncwarp();
