@@ -222,6 +222,9 @@ def run_ours(args):
         raise SystemExit("bench.py needs a GPU: the CUDA path has no CPU fallback")
     torch.cuda.set_device(local)
     if world > 1:
+        # keep stdout to the one JSON line: NCCL prints its version banner there at VERSION level
+        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     w = workload_spec(args)
     M, v, CT = w["M"], w["v"], w["CT"]

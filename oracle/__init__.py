@@ -13,6 +13,13 @@ Two layers live here:
   the Makefile when the reference tree is present.  It pins the closest-centroid
   search of the restatement bit for bit.
 
+* ``_ref/libref_amm_host.so`` + ``_ref/dpu_kernel_*.so`` - the reference's whole AMM
+  (``amm_host.cpp``, ``index_calc_host.cpp``, ``pim_lut_host.cpp`` and the DPU kernel
+  ``src/dpu/pim_lut_kernel.c``, all unmodified) running on host threads through the
+  functional UPMEM stand-in in ``upmem_shim/``.  It pins the LUT gather-accumulate and
+  the dequantisation of the restatement against the reference's own code
+  (`RefAmm`, `build_ref_kernel`).
+
 A third, numpy-only statement of the search (`numpy_index_calculation`) exists so the
 C restatement is cross-checked by an independent implementation on small cases.
 
@@ -31,6 +38,8 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB_PATH = os.path.join(_HERE, "liblutamm_oracle.so")
 _REF_PATH = os.path.join(_HERE, "_ref", "libref_index_calc.so")
+_REF_AMM_PATH = os.path.join(_HERE, "_ref", "libref_amm_host.so")
+_REF_TREE = os.environ.get("LUTAMM_REFERENCE_DIR", "/root/reference")
 
 _u32 = ctypes.c_uint32
 _fp = ctypes.POINTER(ctypes.c_float)
@@ -43,9 +52,14 @@ def build(force: bool = False) -> None:
     """Compile the C restatement (and the reference object when its tree is present)."""
     need = force or not os.path.exists(_LIB_PATH) or (
         os.path.getmtime(_LIB_PATH) < os.path.getmtime(os.path.join(_HERE, "lutamm_oracle.c")))
-    ref_tree = os.path.exists("/root/reference/inference-engine/src/host/index_calc_host.cpp")
-    if need or (ref_tree and not os.path.exists(_REF_PATH)):
-        subprocess.run(["make", "-C", _HERE, "all"], check=True, stdout=subprocess.DEVNULL)
+    if need or (have_reference_tree() and not (os.path.exists(_REF_PATH) and os.path.exists(_REF_AMM_PATH))):
+        subprocess.run(["make", "-C", _HERE, "all", "REF=" + _REF_TREE], check=True, stdout=subprocess.DEVNULL)
+    if have_reference_tree():
+        build_ref_cases()
+
+
+def have_reference_tree() -> bool:
+    return os.path.exists(os.path.join(_REF_TREE, "inference-engine/src/host/index_calc_host.cpp"))
 
 
 _lib = None
@@ -232,3 +246,172 @@ def numpy_index_calculation(x, centroid) -> np.ndarray:
         mn = np.where(take, dist[..., c], mn)
         best = np.where(take, np.uint16(c), best)
     return best
+
+
+# ---------------------------------------------------------------------------------------
+# The reference's whole AMM on the UPMEM stand-in (upmem_shim/): unmodified reference code.
+# ---------------------------------------------------------------------------------------
+class RefIndexCalcParams(ctypes.Structure):
+    """The reference's IndexCalcParams, field for field (src/host/defines.h:12-24)."""
+    _fields_ = [(n, _u32) for n in ("n", "input_feature_len", "sub_vec_len", "num_codebook", "num_centroid",
+                                    "num_threads", "n_stile_size", "cb_mtile_size")]
+
+
+class RefLUTParams(ctypes.Structure):
+    """The reference's LUTParams, field for field (src/host/defines.h:26-50)."""
+    _fields_ = [("n", _u32), ("output_feature_len", _u32), ("num_codebook", _u32), ("num_centroid", _u32),
+                ("scale", ctypes.c_float), ("bias", ctypes.c_float), ("num_threads", _u32), ("dpu_num", _u32),
+                ("input_parallelism", _u32), ("lut_parallelism", _u32), ("feature_stile_size", _u32),
+                ("n_stile_size", _u32), ("n_mtile_size", _u32), ("feature_mtile_size", _u32),
+                ("cb_mtile_size", _u32), ("lut_load_type", _u32), ("feature_load_tile_size", _u32),
+                ("cb_load_tile_size", _u32)]
+
+
+LOOP_ORDERS = ("NFC", "NCF", "FNC", "FCN", "CNF", "CFN")   # src/dpu/CMakeLists.txt:28-40
+LOAD_STATIC, LOAD_FINE_GRAIN, LOAD_COARSE_GRAIN = 0, 1, 2  # enum LUTLoadType, src/host/defines.h:10
+
+
+def ref_kernel_path(CB, CT, loop_order, load_type, n_stile, f_stile, n_mtile, f_mtile, cb_mtile, f_load, cb_load,
+                    nr_tasklets=16) -> str:
+    name = "dpu_kernel_cb%d_ct%d_%s_l%d_s%dx%d_m%dx%dx%d_t%dx%d_k%d.so" % (
+        CB, CT, LOOP_ORDERS[loop_order], load_type, n_stile, f_stile, n_mtile, f_mtile, cb_mtile, f_load, cb_load,
+        nr_tasklets)
+    return os.path.join(_HERE, "_ref", name)
+
+
+def build_ref_kernel(CB, CT, loop_order, load_type, n_stile, f_stile, n_mtile, f_mtile, cb_mtile, f_load, cb_load,
+                     nr_tasklets=16) -> str:
+    """Compile the reference's DPU kernel for one configuration (the -D list of src/dpu/CMakeLists.txt:20-60)
+    into a host shared object; returns its path.  A prebuilt object is reused."""
+    out = ref_kernel_path(CB, CT, loop_order, load_type, n_stile, f_stile, n_mtile, f_mtile, cb_mtile, f_load,
+                          cb_load, nr_tasklets)
+    if os.path.exists(out):
+        return out
+    if not have_reference_tree():
+        raise FileNotFoundError("reference tree absent and %s was not prebuilt" % os.path.basename(out))
+    defs = ["-DNR_TASKLETS=%d" % nr_tasklets, "-DNUM_CODEBOOK=%d" % CB, "-DNUM_CENTROID=%d" % CT,
+            "-DLOOP_ORDER_" + LOOP_ORDERS[loop_order],
+            "-DN_STILE_SIZE=%d" % n_stile, "-DFEATURE_STILE_SIZE=%d" % f_stile,
+            "-DN_MTILE_SIZE=%d" % n_mtile, "-DFEATURE_MTILE_SIZE=%d" % f_mtile, "-DCB_MTILE_SIZE=%d" % cb_mtile,
+            "-DFEATURE_LOAD_TILE_SIZE=%d" % f_load, "-DCB_LOAD_TILE_SIZE=%d" % cb_load]
+    if load_type == LOAD_STATIC:
+        defs.append("-DSTATIC_LUT_TABLE")
+    elif load_type == LOAD_FINE_GRAIN:
+        defs.append("-DFINE_GRAIN")
+    subprocess.run(["make", "-C", _HERE, "ref_kernel", "REF=" + _REF_TREE, "KOUT=" + out, "KDEFS=" + " ".join(defs)],
+                   check=True, stdout=subprocess.DEVNULL)
+    return out
+
+
+def have_ref_amm() -> bool:
+    return os.path.exists(_REF_AMM_PATH)
+
+
+_ref_amm = None
+
+
+def _ref_amm_lib() -> ctypes.CDLL:
+    global _ref_amm
+    if _ref_amm is None:
+        R = ctypes.CDLL(_REF_AMM_PATH)
+        R.ref_amm_open.argtypes = [_u32, ctypes.c_char_p]
+        R.ref_amm_open.restype = ctypes.c_void_p
+        R.ref_amm_run.argtypes = [ctypes.c_void_p, _fp, _fp, _i8p, _fp, _fp,
+                                  ctypes.POINTER(RefIndexCalcParams), ctypes.POINTER(RefLUTParams)]
+        R.ref_amm_run.restype = None
+        R.ref_amm_close.argtypes = [ctypes.c_void_p]
+        R.ref_amm_close.restype = None
+        _ref_amm = R
+    return _ref_amm
+
+
+class RefAmm:
+    """One AMM operator of the reference, run by the reference's own amm_host() and DPU kernel.
+
+    The mapping parameters are those of the reference's YAML (`lut_params`, config/amm.yaml):
+    the token axis is cut into `input_parallelism` = M / n_stile blocks, the output features
+    into `lut_parallelism` = N / f_stile blocks, one DPU per (token block, feature block).
+    """
+
+    def __init__(self, M, N, CB, CT, v, *, loop_order=0, load_type=LOAD_COARSE_GRAIN, n_stile, f_stile, n_mtile,
+                 f_mtile, cb_mtile, f_load, cb_load, nr_tasklets=16, scale=1.0, lut_bias=0.0, nthreads=None):
+        assert M % n_stile == 0 and N % f_stile == 0
+        self.M, self.N, self.CB, self.CT, self.v = M, N, CB, CT, v
+        self.load_type = load_type
+        nthreads = nthreads or default_threads()
+        ip_par, lut_par = M // n_stile, N // f_stile
+        self.ip = RefIndexCalcParams(M, CB * v, v, CB, CT, nthreads, n_stile, cb_mtile)
+        self.lp = RefLUTParams(M, N, CB, CT, scale, lut_bias, nthreads, ip_par * lut_par, ip_par, lut_par,
+                               f_stile, n_stile, n_mtile, f_mtile, cb_mtile, load_type, f_load, cb_load)
+        kernel = build_ref_kernel(CB, CT, loop_order, load_type, n_stile, f_stile, n_mtile, f_mtile, cb_mtile,
+                                  f_load, cb_load, nr_tasklets)
+        self._h = _ref_amm_lib().ref_amm_open(ip_par * lut_par, kernel.encode())
+        # output position of element (i, j) in the DPU-tiled result (test/test_amm.cpp:193-202)
+        i = np.arange(M, dtype=np.int64)[:, None]
+        j = np.arange(N, dtype=np.int64)[None, :]
+        dpu = (i // n_stile) * lut_par + j // f_stile
+        jd = j % f_stile
+        self._where = (dpu * n_stile * f_stile + (jd // f_mtile) * n_stile * f_mtile
+                       + (i % n_stile) * f_mtile + jd % f_mtile)
+
+    def dpu_lut(self, lut: np.ndarray) -> np.ndarray:
+        """Canonical [CB][CT][N] table -> the DPU layout of reorder_pim_lut (test/test_amm.cpp:71-121)."""
+        tile = self.lp.feature_stile_size if self.load_type == LOAD_STATIC else self.lp.feature_load_tile_size
+        return reorder_lut(lut, tile)
+
+    def run_tiled(self, x, centroid, lut_dpu, bias) -> np.ndarray:
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        centroid = np.ascontiguousarray(centroid, dtype=np.float32)
+        bias = np.ascontiguousarray(bias, dtype=np.float32)
+        assert x.shape == (self.M, self.CB * self.v) and centroid.shape == (self.CB, self.CT, self.v)
+        assert lut_dpu.dtype == np.int8 and lut_dpu.size == self.CB * self.CT * self.N and bias.size == self.N
+        out = np.empty(self.M * self.N, dtype=np.float32)
+        _ref_amm_lib().ref_amm_run(self._h, _p(x, _fp), _p(centroid, _fp), _p(lut_dpu, _i8p), _p(bias, _fp),
+                                   _p(out, _fp), ctypes.byref(self.ip), ctypes.byref(self.lp))
+        return out
+
+    def __call__(self, x, centroid, lut, bias) -> np.ndarray:
+        """Canonical tensors in, row-major [M][N] fp32 out."""
+        return self.run_tiled(x, centroid, self.dpu_lut(lut), bias)[self._where]
+
+    def close(self):
+        if self._h:
+            _ref_amm_lib().ref_amm_close(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def _small(lo, lt):
+    return dict(M=64, N=64, CB=16, CT=16, v=4, loop_order=lo, load_type=lt, n_stile=32, f_stile=32, n_mtile=16,
+                f_mtile=16, cb_mtile=8, f_load=8, cb_load=4)
+
+
+# The operator mappings the tests run through the reference's own code.  `build()` compiles the
+# DPU kernel of each while the reference tree is at hand, so the objects travel prebuilt.
+REF_AMM_CASES = {("small_%s_l%d" % (LOOP_ORDERS[lo], lt)): _small(lo, lt) for lo in range(6) for lt in range(3)}
+REF_AMM_CASES.update({
+    # the shape family of the reference's single-kernel example (config/single_kernel_output_example.yaml), shrunk
+    "example_like": dict(M=256, N=256, CB=64, CT=16, v=4, loop_order=1, load_type=LOAD_COARSE_GRAIN, n_stile=128,
+                         f_stile=128, n_mtile=64, f_mtile=32, cb_mtile=32, f_load=8, cb_load=32),
+    # a BERT-base projection (hidden 768, sub-vector 2, 16 centroids) on 12 DPUs
+    "bert_base_proj": dict(M=512, N=768, CB=384, CT=16, v=2, loop_order=1, load_type=LOAD_COARSE_GRAIN, n_stile=256,
+                           f_stile=128, n_mtile=64, f_mtile=32, cb_mtile=128, f_load=8, cb_load=128),
+    "bert_base_proj_static": dict(M=256, N=768, CB=384, CT=16, v=2, loop_order=0, load_type=LOAD_STATIC, n_stile=128,
+                                  f_stile=8, n_mtile=64, f_mtile=8, cb_mtile=128, f_load=8, cb_load=128),
+})
+
+
+def ref_amm_case(name: str, **kw) -> RefAmm:
+    c = dict(REF_AMM_CASES[name])
+    return RefAmm(c.pop("M"), c.pop("N"), c.pop("CB"), c.pop("CT"), c.pop("v"), **c, **kw)
+
+
+def build_ref_cases() -> None:
+    for c in REF_AMM_CASES.values():
+        build_ref_kernel(c["CB"], c["CT"], c["loop_order"], c["load_type"], c["n_stile"], c["f_stile"], c["n_mtile"],
+                         c["f_mtile"], c["cb_mtile"], c["f_load"], c["cb_load"])

@@ -59,12 +59,10 @@ __device__ __forceinline__ size_t tiled_index_offset(uint32_t m, uint32_t cb, ui
 // ------------------------------------------------------------------ reg path
 constexpr int kRegThreads = 128;
 
-// kTok tokens are in flight per thread: their activations are loaded together (one round
-// trip to memory instead of kTok) and their scans interleave, which gives the scheduler
-// kTok independent dependency chains per warp.
-constexpr int kTok = 4;
+// kTok tokens are in flight per thread, which gives the scheduler kTok independent dependency
+// chains per warp.
 
-template <int V, int CT, bool TILED>
+template <int V, int CT, bool TILED, int kTok>
 __global__ void __launch_bounds__(kRegThreads)
 ccs_reg_kernel(const float* __restrict__ x, const float* __restrict__ cent, void* __restrict__ out, uint32_t M,
                uint32_t K, uint32_t CB, uint32_t tokens_per_cta, uint32_t n_stile, uint32_t cb_mtile) {
@@ -242,8 +240,8 @@ ccs_smem_kernel(const float* __restrict__ x, const float* __restrict__ cent, voi
     }
 }
 
-template <int V, int CT>
-cudaError_t run_reg(const CcsArgs& a, cudaStream_t s) {
+template <int V, int CT, int kTok>
+cudaError_t run_reg_tok(const CcsArgs& a, cudaStream_t s) {
     // Default run length per thread: long enough to amortise the centroid load, short enough
     // that a small batch still spreads over the whole GPU (about 8 CTAs of 4 warps per SM).
     uint32_t tpt = a.tokens_per_thread;
@@ -257,12 +255,19 @@ cudaError_t run_reg(const CcsArgs& a, cudaStream_t s) {
     tpt = (tpt + kTok - 1) / kTok * kTok;
     dim3 grid((a.CB + kRegThreads - 1) / kRegThreads, (a.M + tpt - 1) / tpt);
     if (a.format == LUTAMM_INDEX_U16_TILED)
-        ccs_reg_kernel<V, CT, true><<<grid, kRegThreads, 0, s>>>(a.x, a.centroid, a.idx_out, a.M, a.K, a.CB, tpt,
-                                                                   a.n_stile, a.cb_mtile);
+        ccs_reg_kernel<V, CT, true, kTok><<<grid, kRegThreads, 0, s>>>(a.x, a.centroid, a.idx_out, a.M, a.K, a.CB, tpt,
+                                                                         a.n_stile, a.cb_mtile);
     else
-        ccs_reg_kernel<V, CT, false><<<grid, kRegThreads, 0, s>>>(a.x, a.centroid, a.idx_out, a.M, a.K, a.CB, tpt,
-                                                                    a.n_stile, a.cb_mtile);
+        ccs_reg_kernel<V, CT, false, kTok><<<grid, kRegThreads, 0, s>>>(a.x, a.centroid, a.idx_out, a.M, a.K, a.CB, tpt,
+                                                                          a.n_stile, a.cb_mtile);
     return cudaGetLastError();
+}
+
+template <int V, int CT>
+cudaError_t run_reg(const CcsArgs& a, cudaStream_t s) {
+    // Four tokens in flight per thread: their activations are loaded together (one round trip to
+    // memory instead of four) and their scans interleave.  Two or one measured no faster.
+    return run_reg_tok<V, CT, 4>(a, s);
 }
 
 template <int V>

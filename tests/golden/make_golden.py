@@ -11,6 +11,13 @@ the dequantisation expression of inference-engine/src/host/pim_lut_host.cpp:201,
 with numpy fp32 scalars (one rounding per operation) - independently of the C oracle, so
 that the oracle is checked against these files rather than against itself.
 
+The `refamm_*` files additionally hold `out_ref` / `out_ref_tiled`: the output of the reference's
+WHOLE operator - amm_host.cpp, index_calc_host.cpp, pim_lut_host.cpp and the DPU kernel
+src/dpu/pim_lut_kernel.c, all unmodified - run on host threads through the functional UPMEM
+stand-in in oracle/upmem_shim (row-major, and in the DPU-tiled order the reference returns), with
+the mapping parameters stored beside them.  The generator asserts that it is bit-identical to the
+numpy derivation above.
+
 Each .npz holds the inputs too, so the fixtures are self-contained on machines without
 the reference tree.
 """
@@ -79,6 +86,26 @@ def emit(name, x, cent, lut, bias, scale, lut_bias, n_stile=None, cb_mtile=None)
     print(f"{name}: M={M} K={K} v={v} CT={CT} N={lut.shape[2]} idx-hist-head={np.bincount(idx.ravel(), minlength=CT)[:4]}")
 
 
+def emit_refamm(name, case_name, seed, scale, lut_bias, reference_style=False):
+    cfg = dict(oracle.REF_AMM_CASES[case_name])
+    M, N, CB, CT, v = (cfg[k] for k in ("M", "N", "CB", "CT", "v"))
+    c = synth.make_case(M=M, K=CB * v, N=N, v=v, CT=CT, seed=seed, scale=scale, lut_bias=lut_bias,
+                        reference_style=reference_style)
+    r = oracle.ref_amm_case(case_name, scale=scale, lut_bias=lut_bias, nthreads=4)
+    tiled = r.run_tiled(c.x, c.centroid, r.dpu_lut(c.lut), c.bias)
+    out_ref = tiled[r._where]
+    r.close()
+    idx = oracle.ref_index_calculation(c.x, c.centroid, None, None, nthreads=4).reshape(M, CB)
+    acc, out = derive(idx, c.lut, c.bias, scale, lut_bias)
+    assert np.array_equal(out.view(np.uint32), out_ref.view(np.uint32)), "numpy derivation != reference operator"
+    mapping = {k: np.uint32(cfg[k]) for k in ("loop_order", "load_type", "n_stile", "f_stile", "n_mtile", "f_mtile",
+                                               "cb_mtile", "f_load", "cb_load")}
+    np.savez_compressed(os.path.join(OUT, name + ".npz"), x=c.x, centroid=c.centroid, lut=c.lut, bias=c.bias,
+                        scale=np.float32(scale), lut_bias=np.float32(lut_bias), idx=idx, acc=acc, out=out,
+                        out_ref=out_ref, out_ref_tiled=tiled, **mapping)
+    print(f"{name}: reference operator {case_name} M={M} N={N} CB={CB} CT={CT} v={v}: bit-identical to derivation")
+
+
 def main():
     assert oracle.have_reference(), "oracle/_ref is missing: run `make -C oracle` with the reference tree mounted"
     cases = [
@@ -107,6 +134,11 @@ def main():
     c.x[2, 8:10] = -np.inf
     c.centroid[3, 2, 0] = np.nan
     emit("nonfinite_v2_ct8", c.x, c.centroid, c.lut, c.bias, c.scale, c.lut_bias)
+    # the reference's whole operator (host code + DPU kernel), three loop-order / load-type corners
+    assert oracle.have_ref_amm(), "oracle/_ref/libref_amm_host.so is missing"
+    emit_refamm("refamm_ncf_coarse", "small_NCF_l2", 51, 0.1, 0.2, reference_style=True)
+    emit_refamm("refamm_fnc_static", "small_FNC_l0", 52, 0.013, -0.4)
+    emit_refamm("refamm_cfn_fine", "small_CFN_l1", 53, 0.05, 0.0)
 
 
 if __name__ == "__main__":

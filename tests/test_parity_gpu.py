@@ -143,6 +143,38 @@ def test_reference_tiled_layouts(ctx):
     ctx.unload_weights(5)
 
 
+@pytest.mark.parametrize("name", ["small_NCF_l2", "small_FNC_l0", "example_like", "bert_base_proj",
+                                  "bert_base_proj_static"])
+def test_against_the_reference_operator(ctx, name):
+    """The CUDA path against the reference's own amm_host() + DPU kernel (unmodified sources on the
+    functional UPMEM stand-in, prebuilt into oracle/_ref): same parameter blocks, and with the
+    tiled-output flag the very bytes the reference returns."""
+    if not oracle.have_ref_amm():
+        pytest.skip("oracle/_ref (built from the reference tree) absent")
+    cfg = oracle.REF_AMM_CASES[name]
+    M, N, CB, CT, v = (cfg[k] for k in ("M", "N", "CB", "CT", "v"))
+    scale, lut_bias = 0.1, 0.2                      # the reference example's quantisation factors
+    c = synth.make_case(M=M, K=CB * v, N=N, v=v, CT=CT, seed=77, scale=scale, lut_bias=lut_bias, reference_style=True)
+    r = oracle.ref_amm_case(name, scale=scale, lut_bias=lut_bias)
+    try:
+        ref_tiled = r.run_tiled(c.x, c.centroid, r.dpu_lut(c.lut), c.bias)
+        where = r._where
+    finally:
+        r.close()
+    ip, lp = P.make_params(M, CB * v, N, CB, CT, scale, lut_bias, n_stile=cfg["n_stile"], f_stile=cfg["f_stile"],
+                           n_mtile=cfg["n_mtile"], f_mtile=cfg["f_mtile"], cb_mtile=cfg["cb_mtile"])
+    ctx.load_weights(6, c.centroid, c.lut, c.bias, scale, lut_bias, ip, lp)
+    for pname, plan in variants_for(CT, N, CB):
+        ctx.set_plan(6, **plan)
+        y = np.zeros(M * N, dtype=np.float32)
+        ctx.amm_host(6, c.x, y, n_tokens=M, flags=P.FLAG_OUTPUT_TILED)
+        assert np.array_equal(y.view(np.uint32), ref_tiled.view(np.uint32)), f"{pname}: tiled bytes differ"
+        y2 = np.zeros((M, N), dtype=np.float32)
+        ctx.amm_host(6, c.x, y2)
+        assert np.array_equal(y2.view(np.uint32), ref_tiled[where].view(np.uint32)), f"{pname}: row-major bytes differ"
+    ctx.unload_weights(6)
+
+
 def test_argument_validation(ctx):
     c = synth.make_case(M=4, K=32, N=16, v=2, CT=8, seed=1)
     with pytest.raises(P.LutAmmError) as e:
