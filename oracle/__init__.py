@@ -24,8 +24,10 @@ A third, numpy-only statement of the search (`numpy_index_calculation`) exists s
 C restatement is cross-checked by an independent implementation on small cases.
 
 Parity status: closest-centroid search pinned against the unmodified reference source
-and the committed golden vectors generated from it; gather is exact integer addition;
-dequantisation follows ``pim_lut_host.cpp:201`` operation by operation.
+and the committed golden vectors generated from it; gather-accumulate and dequantisation
+(``pim_lut_host.cpp:201``, restated operation by operation) pinned bit for bit against the
+unmodified reference operator on the UPMEM stand-in, for all six loop orders and three LUT
+load types of the DPU kernel.
 """
 from __future__ import annotations
 

@@ -8,8 +8,11 @@
  * Parity status: the closest-centroid search is pinned bit-for-bit against the
  * reference's own, unmodified index_calc_host.cpp (built into oracle/_ref by the
  * Makefile beside this file) and against the golden vectors generated from it.
- * The gather is integer addition (order-free, exact by construction); the
- * dequantisation follows the reference expression operation by operation.
+ * The gather (integer addition, order-free) and the dequantisation (restated
+ * operation by operation) are pinned bit-for-bit against the reference's whole
+ * operator - amm_host.cpp, pim_lut_host.cpp and the DPU kernel pim_lut_kernel.c,
+ * unmodified - run on the functional UPMEM stand-in in upmem_shim/, for all six
+ * loop orders and three LUT load types (tests/test_reference_operator.py).
  *
  * Reference files followed (paths inside the reference project):
  *   inference-engine/src/host/index_calc_host.cpp:8-53   closest-centroid search
