@@ -152,6 +152,21 @@ int lutamm_load_weights(lutamm_ctx* ctx, int layer_id,
 
 int lutamm_unload_weights(lutamm_ctx* ctx, int layer_id);
 
+/* Build one linear layer's int8 lookup table from its centroids and its dense weight on the GPU.
+ * Replaces the table construction of the reference's weight converter
+ * (model-calibration/pim_weight_converter.py:21-36 lut_quant, :83-91 bmm + view):
+ *   lut_f[cb][ct][n] = sum_d centroid[cb][ct][d] * weight[cb*v + d][n]   fp32, d ascending, unfused
+ *   scale = max|lut_f| / 127 (zero point 0),  lut = int8(rint(clamp(lut_f / scale, -128, 127))),
+ *   lut_bias = -scale * 0.
+ * centroid [CB][CT][v] fp32, weight [CB*v][N] fp32 row-major (the checkpoint's layout), lut_out
+ * [CB][CT][N] int8: each may be host or device memory; scale_out and lut_bias_out are host floats.
+ * N must be a multiple of 4, v <= 32.  Synchronous.  The reference's bmm runs in whatever order its
+ * BLAS picks, so against it the table agrees to one int8 step at rounding boundaries; against the
+ * stated order it is exact. */
+int lutamm_build_lut(lutamm_ctx* ctx, const float* centroid, const float* weight,
+                     uint32_t num_codebook, uint32_t num_centroid, uint32_t sub_vec_len,
+                     uint32_t output_feature_len, int8_t* lut_out, float* scale_out, float* lut_bias_out);
+
 /* ---- the operator ---------------------------------------------------------------- */
 
 /* Replaces amm_host() (src/host/amm_host.cpp:10-30; declared amm_host.h:8-10):

@@ -417,3 +417,27 @@ def build_ref_cases() -> None:
     for c in REF_AMM_CASES.values():
         build_ref_kernel(c["CB"], c["CT"], c["loop_order"], c["load_type"], c["n_stile"], c["f_stile"], c["n_mtile"],
                          c["f_mtile"], c["cb_mtile"], c["f_load"], c["cb_load"])
+
+
+# ---------------------------------------------------------------------------------------
+# Load-time table construction (model-calibration/pim_weight_converter.py:21-36, 83-91).
+# ---------------------------------------------------------------------------------------
+def build_lut(centroid, weight):
+    """lut_f = bmm(centroid [CB][CT][v], weight.view(CB, v, N)) in fp32 with the sub-vector
+    dimension accumulated in ascending order, one rounding per operation; then the converter's
+    symmetric quantisation: scale = max|lut_f| / 127, lut = int8(rint(clip(lut_f / scale, -128, 127))),
+    lut_bias = -scale * 0.  Returns (lut int8 [CB][CT][N], scale fp32, lut_bias fp32)."""
+    centroid = np.ascontiguousarray(centroid, dtype=np.float32)
+    weight = np.ascontiguousarray(weight, dtype=np.float32)
+    CB, CT, v = centroid.shape
+    N = weight.shape[1]
+    w = weight.reshape(CB, v, N)
+    acc = np.zeros((CB, CT, N), dtype=np.float32)
+    for d in range(v):
+        acc = acc + centroid[:, :, d, None] * w[:, None, d, :]   # numpy fp32: multiply, then add, each rounded
+    scale = np.float32(np.abs(acc).max()) / np.float32(127.0)
+    if scale > 0:
+        lut = np.rint(np.clip(acc / scale, np.float32(-128), np.float32(127))).astype(np.int8)
+    else:
+        lut = np.zeros((CB, CT, N), dtype=np.int8)
+    return lut, np.float32(scale), np.float32(-scale * np.float32(0.0))

@@ -28,7 +28,7 @@ ABI_SYMBOLS = [
     "lutamm_version", "lutamm_load_weights", "lutamm_unload_weights", "lutamm_amm", "lutamm_amm_debug",
     "lutamm_index_calculation", "lutamm_pim_lut", "lutamm_set_plan", "lutamm_get_plan", "lutamm_tune",
     "lutamm_enable_timing", "lutamm_get_timings", "lutamm_launch_count",
-    "lutamm_amm_static_scratch", "lutamm_static_scratch_last_error",
+    "lutamm_amm_static_scratch", "lutamm_static_scratch_last_error", "lutamm_build_lut",
 ]
 
 
@@ -99,6 +99,8 @@ def load_library() -> ctypes.CDLL:
     L.lutamm_last_error.restype = ctypes.c_char_p
     L.lutamm_load_weights.argtypes = [vp, i32, vp, vp, vp, ctypes.POINTER(IndexCalcParams), ctypes.POINTER(LUTParams)]
     L.lutamm_unload_weights.argtypes = [vp, i32]
+    L.lutamm_build_lut.argtypes = [vp, vp, vp, u32, u32, u32, u32, vp, ctypes.POINTER(ctypes.c_float),
+                                   ctypes.POINTER(ctypes.c_float)]
     L.lutamm_amm.argtypes = [vp, i32, vp, vp, u32, u32]
     L.lutamm_amm_debug.argtypes = [vp, i32, vp, vp, u32, vp, vp, u32]
     L.lutamm_index_calculation.argtypes = [vp, i32, vp, vp, u32, u32]
@@ -227,6 +229,21 @@ class LutAmmContext:
         self._check(self._L.lutamm_load_weights(self._h, layer_id, _ptr(centroid), _ptr(lut), _ptr(bias),
                                                 ctypes.byref(ip), ctypes.byref(lp)))
         self.layers[layer_id] = _LayerInfo(K, N, CB, CT, ip, lp)
+
+    def build_lut(self, centroid, weight, lut_out=None):
+        """The table construction of the reference's converter (model-calibration/pim_weight_converter.py:21-36,
+        83-91) on the GPU.  centroid [CB][CT][v] fp32, weight [CB*v][N] fp32 (numpy or torch, host or device);
+        returns (lut int8 [CB][CT][N], scale, lut_bias)."""
+        CB, CT, v = (int(d) for d in centroid.shape)
+        K, N = (int(d) for d in weight.shape)
+        if K != CB * v:
+            raise ValueError("weight rows must equal num_codebook * sub_vec_len")
+        if lut_out is None:
+            lut_out = np.empty((CB, CT, N), dtype=np.int8)
+        scale, lut_bias = ctypes.c_float(), ctypes.c_float()
+        self._check(self._L.lutamm_build_lut(self._h, _ptr(centroid), _ptr(weight), CB, CT, v, N, _ptr(lut_out),
+                                             ctypes.byref(scale), ctypes.byref(lut_bias)))
+        return lut_out, float(scale.value), float(lut_bias.value)
 
     def unload_weights(self, layer_id: int):
         self._check(self._L.lutamm_unload_weights(self._h, layer_id))

@@ -41,12 +41,26 @@ def cuda_sources() -> list[str]:
 
 
 def build_cuda(force: bool = False, verbose: bool = False) -> str:
+    """One object per .cu (compiled in parallel, rebuilt only when it or a header changed), then one link."""
     srcs = cuda_sources()
-    deps = srcs + glob.glob(os.path.join(CSRC, "*.cuh")) + glob.glob(os.path.join(CSRC, "*.h")) + \
+    hdrs = glob.glob(os.path.join(CSRC, "*.cuh")) + glob.glob(os.path.join(CSRC, "*.h")) + \
         [os.path.join(HERE, "..", "include", "lutamm.h")]
-    if force or _stale(LIB, deps):
-        cmd = [_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-o", LIB] + srcs
-        subprocess.run(cmd, check=True)
+    objdir = os.path.join(CSRC, "build")
+    os.makedirs(objdir, exist_ok=True)
+    compile_flags = [f for f in NVCC_FLAGS if f not in ("-shared", "-cudart", "static")]
+    jobs, objs = [], []
+    for src in srcs:
+        obj = os.path.join(objdir, os.path.splitext(os.path.basename(src))[0] + ".o")
+        objs.append(obj)
+        if force or _stale(obj, [src] + hdrs):
+            cmd = [_nvcc()] + compile_flags + (["-Xptxas", "-v"] if verbose else []) + ["-c", "-o", obj, src]
+            jobs.append((src, subprocess.Popen(cmd)))
+    failed = [src for src, p in jobs if p.wait() != 0]
+    if failed:
+        raise RuntimeError("nvcc failed for " + ", ".join(os.path.basename(f) for f in failed))
+    if jobs or _stale(LIB, objs):
+        subprocess.run([_nvcc(), "-shared", "-cudart", "static", "-gencode", "arch=compute_100a,code=sm_100a",
+                        "-o", LIB] + objs, check=True)
     return LIB
 
 

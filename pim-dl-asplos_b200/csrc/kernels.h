@@ -71,6 +71,19 @@ uint32_t umma_auto_split(uint32_t M, uint32_t CB, uint32_t CT, uint32_t N, uint3
 // LUT [CB*CT][N] -> [N][CB*CT]
 cudaError_t launch_transpose_lut(const int8_t* lut, int8_t* lut_t, uint32_t rows, uint32_t cols, cudaStream_t s);
 
+// ---- load time: int8 table from centroids x dense weight -------------------------------
+struct LutBuildArgs {
+    const float* centroid;  // [CB][CT][v]
+    const float* weight;    // [K = CB*v][N], row-major
+    int8_t* lut;            // out: [CB][CT][N]
+    uint32_t* absmax_bits;  // device scratch word
+    float* scale_out;       // device, one float
+    float* lut_bias_out;    // device, one float
+    uint32_t CB, CT, v, N;
+};
+// Three launches on `s`: abs-max pass, quantising pass, scalar finish.
+cudaError_t launch_lut_build(const LutBuildArgs& a, cudaStream_t s, const char** why);
+
 // Driver entry point for tensor-map encoding, resolved through the runtime so the library
 // carries no link-time dependency on the driver and loads on machines without one.
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,

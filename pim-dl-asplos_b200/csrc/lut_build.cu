@@ -1,0 +1,112 @@
+// Load-time construction of a layer's int8 lookup table from its centroids and its dense
+// weight: what model-calibration/pim_weight_converter.py:21-36,83-91 of the reference does with
+// torch.bmm + lut_quant, as two HBM-bound passes that never materialise the fp32 table.
+//
+//   lut_f[cb][ct][n] = sum_d centroid[cb][ct][d] * weight[cb*v + d][n]     (fp32, d ascending, unfused)
+//   scale            = max|lut_f| / 127                                    (zero point 0)
+//   lut[cb][ct][n]   = int8( rint( clamp( lut_f / scale, -128, 127 ) ) )   (round half to even)
+//
+// Pass 1 reduces max|lut_f|; pass 2 recomputes the products and writes the bytes.  Compulsory
+// traffic: the weight twice (8*K*N bytes) plus the table once (CB*CT*N bytes).
+#include "kernels.h"
+
+namespace lutamm {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kMaxV = 32;
+
+// One block: one codebook x one chunk of kThreads*4 output columns.  A thread owns four
+// adjacent columns (one 16-byte weight load per sub-vector dimension, one 4-byte table
+// store per centroid, so a warp writes 128 contiguous bytes per centroid row).
+template <bool kWrite>
+__global__ void __launch_bounds__(kThreads)
+lut_build_kernel(const float* __restrict__ centroid, const float* __restrict__ weight, int8_t* __restrict__ lut,
+                 uint32_t* __restrict__ absmax_bits, uint32_t CT, uint32_t v, uint32_t N) {
+    extern __shared__ float s_cent[];  // [CT][v]
+    const uint32_t cb = blockIdx.y;
+    for (uint32_t i = threadIdx.x; i < CT * v; i += kThreads) s_cent[i] = centroid[(size_t)cb * CT * v + i];
+    __syncthreads();
+
+    const uint32_t n0 = (blockIdx.x * kThreads + threadIdx.x) * 4;
+    float amax = 0.f;
+    if (n0 < N) {
+        float4 w[kMaxV];
+        const float* wrow = weight + (size_t)cb * v * N + n0;
+#pragma unroll
+        for (int d = 0; d < kMaxV; ++d)
+            if (d < (int)v) w[d] = *reinterpret_cast<const float4*>(wrow + (size_t)d * N);
+        float scale = 1.f;
+        if (kWrite) scale = __fdiv_rn(__uint_as_float(*absmax_bits), 127.f);
+        for (uint32_t ct = 0; ct < CT; ++ct) {
+            float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int d = 0; d < kMaxV; ++d)
+                if (d < (int)v) {
+                    const float c = s_cent[ct * v + d];
+                    a.x = __fadd_rn(a.x, __fmul_rn(c, w[d].x));
+                    a.y = __fadd_rn(a.y, __fmul_rn(c, w[d].y));
+                    a.z = __fadd_rn(a.z, __fmul_rn(c, w[d].z));
+                    a.w = __fadd_rn(a.w, __fmul_rn(c, w[d].w));
+                }
+            if (!kWrite) {
+                amax = fmaxf(amax, fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(a.z), fabsf(a.w))));
+            } else {
+                auto q = [scale](float x) -> int {
+                    const float r = __fdiv_rn(x, scale);
+                    return (int)rintf(fminf(fmaxf(r, -128.f), 127.f));
+                };
+                char4 o;
+                if (scale > 0.f) {
+                    o.x = (signed char)q(a.x); o.y = (signed char)q(a.y);
+                    o.z = (signed char)q(a.z); o.w = (signed char)q(a.w);
+                } else {
+                    o = make_char4(0, 0, 0, 0);  // an all-zero table has no scale; the reference would emit NaN bytes
+                }
+                *reinterpret_cast<char4*>(lut + ((size_t)cb * CT + ct) * N + n0) = o;
+            }
+        }
+    }
+    if (!kWrite) {
+        // non-negative floats order like their bit patterns
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        __shared__ float s_w[kThreads / 32];
+        if ((threadIdx.x & 31) == 0) s_w[threadIdx.x >> 5] = amax;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float m = s_w[0];
+            for (int i = 1; i < kThreads / 32; ++i) m = fmaxf(m, s_w[i]);
+            if (m == m) atomicMax(absmax_bits, __float_as_uint(m));
+        }
+    }
+}
+
+__global__ void lut_build_finish_kernel(const uint32_t* absmax_bits, float* scale_out, float* lut_bias_out) {
+    const float scale = __fdiv_rn(__uint_as_float(*absmax_bits), 127.f);
+    *scale_out = scale;
+    *lut_bias_out = -scale * 0.f;  // -scale * zero_point, zero_point = 0 (pim_weight_converter.py:35)
+}
+
+}  // namespace
+
+cudaError_t launch_lut_build(const LutBuildArgs& a, cudaStream_t s, const char** why) {
+    *why = nullptr;
+    if (a.v == 0 || a.v > kMaxV) { *why = "sub-vector length must be 1..32"; return cudaErrorInvalidValue; }
+    if (a.CB == 0 || a.CB > 65535 || a.CT == 0) { *why = "num_codebook must be 1..65535 and num_centroid non-zero"; return cudaErrorInvalidValue; }
+    if (a.N % 4 != 0) { *why = "output features must be a multiple of 4"; return cudaErrorInvalidValue; }
+    if ((reinterpret_cast<uintptr_t>(a.weight) & 15) || (reinterpret_cast<uintptr_t>(a.lut) & 3)) {
+        *why = "weight must be 16-byte aligned, table 4-byte aligned"; return cudaErrorInvalidValue;
+    }
+    const size_t smem = (size_t)a.CT * a.v * sizeof(float);
+    if (smem > 48 * 1024) { *why = "centroids of one codebook exceed 48 KB"; return cudaErrorInvalidValue; }
+    cudaError_t e = cudaMemsetAsync(a.absmax_bits, 0, sizeof(uint32_t), s);
+    if (e != cudaSuccess) return e;
+    const dim3 grid((a.N / 4 + kThreads - 1) / kThreads, a.CB);
+    lut_build_kernel<false><<<grid, kThreads, smem, s>>>(a.centroid, a.weight, nullptr, a.absmax_bits, a.CT, a.v, a.N);
+    lut_build_kernel<true><<<grid, kThreads, smem, s>>>(a.centroid, a.weight, a.lut, a.absmax_bits, a.CT, a.v, a.N);
+    lut_build_finish_kernel<<<1, 1, 0, s>>>(a.absmax_bits, a.scale_out, a.lut_bias_out);
+    return cudaGetLastError();
+}
+
+}  // namespace lutamm

@@ -66,7 +66,7 @@ struct lutamm_ctx {
     cudaStream_t own_stream = nullptr;
     cudaStream_t stream = nullptr;
     std::map<int, Layer> layers;
-    Buf d_in, d_out, d_idx, d_idx16, d_acc_dbg, d_acc_scratch, d_counters;
+    Buf d_in, d_out, d_idx, d_idx16, d_acc_dbg, d_acc_scratch, d_counters, d_build;
     // host-buffer pipeline: copy-in and copy-out streams, two staging slots
     cudaStream_t s_in = nullptr, s_out = nullptr;
     Buf p_in[2], p_out[2];
@@ -453,7 +453,8 @@ int lutamm_destroy(lutamm_ctx* c) {
     }
     if (c->s_in) cudaStreamDestroy(c->s_in);
     if (c->s_out) cudaStreamDestroy(c->s_out);
-    for (Buf* b : {&c->d_in, &c->d_out, &c->d_idx, &c->d_idx16, &c->d_acc_dbg, &c->d_acc_scratch, &c->d_counters})
+    for (Buf* b : {&c->d_in, &c->d_out, &c->d_idx, &c->d_idx16, &c->d_acc_dbg, &c->d_acc_scratch, &c->d_counters,
+                   &c->d_build})
         cudaFree(b->p);
     cudaFree(c->d_err);
     cudaFreeHost(c->h_err);
@@ -515,6 +516,47 @@ int lutamm_load_weights(lutamm_ctx* c, int layer_id, const float* centroid, cons
     CU_TRY(c, cudaMemcpyAsync(L.d_bias, bias, bb, cudaMemcpyDefault, c->stream));
     CU_TRY(c, cudaStreamSynchronize(c->stream));
     L.plan = lutamm_plan{};
+    return LUTAMM_OK;
+}
+
+int lutamm_build_lut(lutamm_ctx* c, const float* centroid, const float* weight, uint32_t CB, uint32_t CT, uint32_t v,
+                     uint32_t N, int8_t* lut_out, float* scale_out, float* lut_bias_out) {
+    if (!c) return fail(nullptr, LUTAMM_EINVAL, "null context");
+    if (!centroid || !weight || !lut_out || !scale_out || !lut_bias_out) return fail(c, LUTAMM_EINVAL, "null argument");
+    if (!CB || !CT || !v || !N) return fail(c, LUTAMM_EINVAL, "zero-sized shape parameter");
+    if (N % 4) return fail(c, LUTAMM_EINVAL, "output_feature_len must be a multiple of 4");
+    DeviceGuard g(c->device);
+    const size_t cen_b = (size_t)CB * CT * v * sizeof(float), w_b = (size_t)CB * v * N * sizeof(float),
+                 lut_b = (size_t)CB * CT * N;
+    // staging for whichever of the three tensors lives in host memory; [0..255] holds the scalars
+    const bool cen_dev = is_device_ptr(centroid), w_dev = is_device_ptr(weight), lut_dev = is_device_ptr(lut_out);
+    const size_t off_cen = 256, off_w = off_cen + (cen_dev ? 0 : (cen_b + 255) / 256 * 256),
+                 off_lut = off_w + (w_dev ? 0 : (w_b + 255) / 256 * 256), total = off_lut + (lut_dev ? 0 : lut_b);
+    if (int rc = ensure(c, c->d_build, total)) return rc;
+    char* base = static_cast<char*>(c->d_build.p);
+    const float* d_cen = centroid;
+    const float* d_w = weight;
+    int8_t* d_lut = lut_out;
+    if (!cen_dev) {
+        CU_TRY(c, cudaMemcpyAsync(base + off_cen, centroid, cen_b, cudaMemcpyHostToDevice, c->stream));
+        d_cen = reinterpret_cast<const float*>(base + off_cen);
+    }
+    if (!w_dev) {
+        CU_TRY(c, cudaMemcpyAsync(base + off_w, weight, w_b, cudaMemcpyHostToDevice, c->stream));
+        d_w = reinterpret_cast<const float*>(base + off_w);
+    }
+    if (!lut_dev) d_lut = reinterpret_cast<int8_t*>(base + off_lut);
+    LutBuildArgs a{d_cen, d_w, d_lut, reinterpret_cast<uint32_t*>(base), reinterpret_cast<float*>(base + 16),
+                   reinterpret_cast<float*>(base + 32), CB, CT, v, N};
+    const char* why = nullptr;
+    cudaError_t e = launch_lut_build(a, c->stream, &why);
+    if (e != cudaSuccess)
+        return fail(c, why ? LUTAMM_EINVAL : LUTAMM_ECUDA, why ? std::string(why) : std::string("lut build: ") + cudaGetErrorString(e));
+    c->launches += 3;
+    if (!lut_dev) CU_TRY(c, cudaMemcpyAsync(lut_out, d_lut, lut_b, cudaMemcpyDeviceToHost, c->stream));
+    CU_TRY(c, cudaMemcpyAsync(scale_out, base + 16, sizeof(float), cudaMemcpyDeviceToHost, c->stream));
+    CU_TRY(c, cudaMemcpyAsync(lut_bias_out, base + 32, sizeof(float), cudaMemcpyDeviceToHost, c->stream));
+    CU_TRY(c, cudaStreamSynchronize(c->stream));
     return LUTAMM_OK;
 }
 
