@@ -160,7 +160,7 @@ int lutamm_unload_weights(lutamm_ctx* ctx, int layer_id);
  *   lut_bias = -scale * 0.
  * centroid [CB][CT][v] fp32, weight [CB*v][N] fp32 row-major (the checkpoint's layout), lut_out
  * [CB][CT][N] int8: each may be host or device memory; scale_out and lut_bias_out are host floats.
- * N must be a multiple of 4, v <= 32.  Synchronous.  The reference's bmm runs in whatever order its
+ * N must be a multiple of 4.  Synchronous.  The reference's bmm runs in whatever order its
  * BLAS picks, so against it the table agrees to one int8 step at rounding boundaries; against the
  * stated order it is exact. */
 int lutamm_build_lut(lutamm_ctx* ctx, const float* centroid, const float* weight,

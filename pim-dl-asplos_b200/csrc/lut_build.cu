@@ -14,16 +14,19 @@ namespace lutamm {
 namespace {
 
 constexpr int kThreads = 256;
-constexpr int kMaxV = 32;
+constexpr int kMaxV = 1024;  // run-time path; bounded by the shared-memory check below
 
 // One block: one codebook x one chunk of kThreads*4 output columns.  A thread owns four
 // adjacent columns (one 16-byte weight load per sub-vector dimension, one 4-byte table
 // store per centroid, so a warp writes 128 contiguous bytes per centroid row).
-template <bool kWrite>
+// V > 0: compile-time sub-vector length, the thread's weight slice lives in registers.
+// V == 0: run-time length, the slice is re-read (L1 resident) per centroid.
+template <int V, bool kWrite>
 __global__ void __launch_bounds__(kThreads)
 lut_build_kernel(const float* __restrict__ centroid, const float* __restrict__ weight, int8_t* __restrict__ lut,
-                 uint32_t* __restrict__ absmax_bits, uint32_t CT, uint32_t v, uint32_t N) {
+                 uint32_t* __restrict__ absmax_bits, uint32_t CT, uint32_t v_rt, uint32_t N) {
     extern __shared__ float s_cent[];  // [CT][v]
+    const uint32_t v = V > 0 ? (uint32_t)V : v_rt;
     const uint32_t cb = blockIdx.y;
     for (uint32_t i = threadIdx.x; i < CT * v; i += kThreads) s_cent[i] = centroid[(size_t)cb * CT * v + i];
     __syncthreads();
@@ -31,29 +34,41 @@ lut_build_kernel(const float* __restrict__ centroid, const float* __restrict__ w
     const uint32_t n0 = (blockIdx.x * kThreads + threadIdx.x) * 4;
     float amax = 0.f;
     if (n0 < N) {
-        float4 w[kMaxV];
         const float* wrow = weight + (size_t)cb * v * N + n0;
+        float4 w[V > 0 ? V : 1];
+        if (V > 0) {
 #pragma unroll
-        for (int d = 0; d < kMaxV; ++d)
-            if (d < (int)v) w[d] = *reinterpret_cast<const float4*>(wrow + (size_t)d * N);
-        float scale = 1.f;
-        if (kWrite) scale = __fdiv_rn(__uint_as_float(*absmax_bits), 127.f);
+            for (int d = 0; d < V; ++d) w[d] = __ldg(reinterpret_cast<const float4*>(wrow + (size_t)d * N));
+        }
+        float scale = 1.f, inv_scale = 1.f;
+        if (kWrite) {
+            scale = __fdiv_rn(__uint_as_float(*absmax_bits), 127.f);
+            inv_scale = __fdiv_rn(1.f, scale);
+        }
         for (uint32_t ct = 0; ct < CT; ++ct) {
             float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+            auto step = [&a](float c, const float4& wd) {
+                a.x = __fadd_rn(a.x, __fmul_rn(c, wd.x));
+                a.y = __fadd_rn(a.y, __fmul_rn(c, wd.y));
+                a.z = __fadd_rn(a.z, __fmul_rn(c, wd.z));
+                a.w = __fadd_rn(a.w, __fmul_rn(c, wd.w));
+            };
+            if (V > 0) {
 #pragma unroll
-            for (int d = 0; d < kMaxV; ++d)
-                if (d < (int)v) {
-                    const float c = s_cent[ct * v + d];
-                    a.x = __fadd_rn(a.x, __fmul_rn(c, w[d].x));
-                    a.y = __fadd_rn(a.y, __fmul_rn(c, w[d].y));
-                    a.z = __fadd_rn(a.z, __fmul_rn(c, w[d].z));
-                    a.w = __fadd_rn(a.w, __fmul_rn(c, w[d].w));
-                }
+                for (int d = 0; d < V; ++d) step(s_cent[ct * V + d], w[d]);
+            } else {
+                for (uint32_t d = 0; d < v; ++d)
+                    step(s_cent[ct * v + d], __ldg(reinterpret_cast<const float4*>(wrow + (size_t)d * N)));
+            }
             if (!kWrite) {
                 amax = fmaxf(amax, fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(a.z), fabsf(a.w))));
             } else {
-                auto q = [scale](float x) -> int {
-                    const float r = __fdiv_rn(x, scale);
+                // rint(x / scale) with the IEEE division only where it can matter: x * (1/scale) is within
+                // a few ulp of the quotient (|r| <= 128, so < 1e-4 absolute), hence both round to the same
+                // integer unless the product lies within 1e-3 of a half-way point.
+                auto q = [scale, inv_scale](float x) -> int {
+                    float r = __fmul_rn(x, inv_scale);
+                    if (fabsf(fabsf(r - floorf(r)) - 0.5f) < 1e-3f) r = __fdiv_rn(x, scale);
                     return (int)rintf(fminf(fmaxf(r, -128.f), 127.f));
                 };
                 char4 o;
@@ -82,6 +97,12 @@ lut_build_kernel(const float* __restrict__ centroid, const float* __restrict__ w
     }
 }
 
+template <int V>
+void launch_both(const LutBuildArgs& a, dim3 grid, size_t smem, cudaStream_t s) {
+    lut_build_kernel<V, false><<<grid, kThreads, smem, s>>>(a.centroid, a.weight, nullptr, a.absmax_bits, a.CT, a.v, a.N);
+    lut_build_kernel<V, true><<<grid, kThreads, smem, s>>>(a.centroid, a.weight, a.lut, a.absmax_bits, a.CT, a.v, a.N);
+}
+
 __global__ void lut_build_finish_kernel(const uint32_t* absmax_bits, float* scale_out, float* lut_bias_out) {
     const float scale = __fdiv_rn(__uint_as_float(*absmax_bits), 127.f);
     *scale_out = scale;
@@ -92,7 +113,7 @@ __global__ void lut_build_finish_kernel(const uint32_t* absmax_bits, float* scal
 
 cudaError_t launch_lut_build(const LutBuildArgs& a, cudaStream_t s, const char** why) {
     *why = nullptr;
-    if (a.v == 0 || a.v > kMaxV) { *why = "sub-vector length must be 1..32"; return cudaErrorInvalidValue; }
+    if (a.v == 0 || a.v > kMaxV) { *why = "sub-vector length must be 1..1024"; return cudaErrorInvalidValue; }
     if (a.CB == 0 || a.CB > 65535 || a.CT == 0) { *why = "num_codebook must be 1..65535 and num_centroid non-zero"; return cudaErrorInvalidValue; }
     if (a.N % 4 != 0) { *why = "output features must be a multiple of 4"; return cudaErrorInvalidValue; }
     if ((reinterpret_cast<uintptr_t>(a.weight) & 15) || (reinterpret_cast<uintptr_t>(a.lut) & 3)) {
@@ -103,8 +124,14 @@ cudaError_t launch_lut_build(const LutBuildArgs& a, cudaStream_t s, const char**
     cudaError_t e = cudaMemsetAsync(a.absmax_bits, 0, sizeof(uint32_t), s);
     if (e != cudaSuccess) return e;
     const dim3 grid((a.N / 4 + kThreads - 1) / kThreads, a.CB);
-    lut_build_kernel<false><<<grid, kThreads, smem, s>>>(a.centroid, a.weight, nullptr, a.absmax_bits, a.CT, a.v, a.N);
-    lut_build_kernel<true><<<grid, kThreads, smem, s>>>(a.centroid, a.weight, a.lut, a.absmax_bits, a.CT, a.v, a.N);
+    switch (a.v) {
+        case 1: launch_both<1>(a, grid, smem, s); break;
+        case 2: launch_both<2>(a, grid, smem, s); break;
+        case 4: launch_both<4>(a, grid, smem, s); break;
+        case 8: launch_both<8>(a, grid, smem, s); break;
+        case 16: launch_both<16>(a, grid, smem, s); break;
+        default: launch_both<0>(a, grid, smem, s); break;
+    }
     lut_build_finish_kernel<<<1, 1, 0, s>>>(a.absmax_bits, a.scale_out, a.lut_bias_out);
     return cudaGetLastError();
 }

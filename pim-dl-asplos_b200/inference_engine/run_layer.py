@@ -119,6 +119,7 @@ def run(args, whole_model: bool):
         print(f"amm time {amm_total * 1e-3 * n_layers:.6f}, non-amm time {max(avg - amm_total * 1e-3 * n_layers, 0):.6f}")
         ctx.enable_timing(False)
     ctx.close()
+    return {"avg_s": avg, "tokens": n, "tokens_per_s": n / avg}
 
 
 if __name__ == '__main__':

@@ -82,7 +82,7 @@ def test_gpu_converter_matches_reference_and_restatement(ctx, tmp_path):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("CB,CT,v,N", [(384, 16, 2, 3072), (96, 32, 8, 768), (64, 8, 4, 20), (5, 5, 3, 36), (8, 256, 1, 64)])
+@pytest.mark.parametrize("CB,CT,v,N", [(384, 16, 2, 3072), (96, 32, 8, 768), (64, 8, 4, 20), (5, 5, 3, 36), (8, 256, 1, 64), (12, 16, 20, 64), (4, 16, 32, 128)])
 def test_gpu_build_lut_shapes(ctx, CB, CT, v, N):
     """Bit-exact against the stated order on BERT-base FFN1 and odd shapes; device-resident operands too."""
     import torch
@@ -112,5 +112,5 @@ def test_gpu_build_lut_rejects_bad_shapes(ctx):
     with pytest.raises(P.LutAmmError) as e:
         ctx.build_lut(np.zeros((4, 8, 2), np.float32), np.zeros((8, 18), np.float32))
     assert e.value.code == P.EINVAL
-    with pytest.raises(P.LutAmmError):
-        ctx.build_lut(np.zeros((2, 4, 33), np.float32), np.zeros((66, 16), np.float32))
+    with pytest.raises(P.LutAmmError):   # one codebook's centroids must fit 48 KB of shared memory
+        ctx.build_lut(np.zeros((1, 256, 64), np.float32), np.zeros((64, 16), np.float32))

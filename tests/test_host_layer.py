@@ -112,3 +112,29 @@ def test_tuned_plans_round_trip(tmp_path):
     transformer_config.save_with_plans(raw, {"ffn1": {"variant": 2, "umma_n_tile": 192, "umma_operand": 2}}, str(out))
     cfg, _ = transformer_config.load(str(out))
     assert cfg["plans"] == {"ffn1": {"variant": 2, "umma_n_tile": 192, "umma_operand": 2}}
+
+
+def test_sensitivity_sweep_configs(tmp_path):
+    """The artifact-evaluation sweep driver generates the reference's shapes
+    (asplos24-ae/sensitivity-analysis/configs) and every config passes the transformer parser."""
+    import os
+    import sys
+    eng = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "pim-dl-asplos_b200", "inference_engine")
+    sys.path.insert(0, eng)
+    import run_experiments as rx
+    import transformer_config
+    rows = rx.main(["--dry_run", "--out_dir", str(tmp_path)])
+    assert len(rows) == 3 * 5 * 3 + 5
+    c = rx.make_config("sub-vector", "bert-base", 8)
+    assert c["kernel_params"]["qkv_num_codebook"] == 96 and c["kernel_params"]["ffn2_num_codebook"] == 384
+    c = rx.make_config("centroid", "bert-base", 128)
+    assert c["kernel_params"]["o_num_codebook"] == 192 and c["kernel_params"]["o_num_centroid"] == 128
+    c = rx.make_config("hidden-dim", "-", 5120)
+    assert c["network_params"]["head_num"] * c["network_params"]["head_dim"] == 5120
+    assert c["kernel_params"]["ffn2_num_codebook"] == 1024 and c["network_params"]["ffn_hidden_dim"] == 20480
+    c = rx.make_config("batch-size", "vit-huge", 8)
+    assert c["network_params"]["batch_size"] == 8 and c["kernel_params"]["qkv_num_codebook"] == 320
+    for f in os.listdir(tmp_path / "configs"):
+        cfg, _ = transformer_config.load(str(tmp_path / "configs" / f))
+        assert cfg["token_dim"] % cfg["num_codebook"]["qkv"] == 0
+    assert rx.reference_cpu_seconds("batch-size", "bert-large", 32) == 2.32561
