@@ -328,6 +328,14 @@ cudaError_t launch_ccs(const CcsArgs& a, cudaStream_t s, const char** why) {
             case 8: return run_smem<8>(a, s);
             case 16: return run_smem<16>(a, s);
             case 32: return run_smem<32>(a, s);
+            // hidden sizes that are not a power of two times the codebook count (2560 / 256, 5120 / 256, ...)
+            case 3: return run_smem<3>(a, s);
+            case 5: return run_smem<5>(a, s);
+            case 6: return run_smem<6>(a, s);
+            case 10: return run_smem<10>(a, s);
+            case 12: return run_smem<12>(a, s);
+            case 20: return run_smem<20>(a, s);
+            case 24: return run_smem<24>(a, s);
             default: break;
         }
     }

@@ -67,18 +67,18 @@ struct UmmaParams {
 __device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t n) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n) : "memory");
 }
-// 64-bit left shift with PTX semantics: a shift amount of 64 or more gives 0 (shl.b64 clamps).
-__device__ __forceinline__ uint64_t shl64_clamped(uint64_t v, uint32_t n) {
-    uint64_t r;
-    asm("shl.b64 %0, %1, %2;" : "=l"(r) : "l"(v), "r"(n));
+// 32-bit left shift with PTX semantics: a shift amount of 32 or more gives 0 (shl.b32 clamps).
+__device__ __forceinline__ uint32_t shl32_clamped(uint32_t v, uint32_t n) {
+    uint32_t r;
+    asm("shl.b32 %0, %1, %2;" : "=r"(r) : "r"(v), "r"(n));
     return r;
 }
-// 16 bytes with byte `i` set to 1, given n = 8*i; any n >= 128 gives zeros.  Two clamped 64-bit
-// shifts: the low half is 1 << n (zero once n >= 64), the high half 1 << (n - 64), where the
-// unsigned wrap-around of n - 64 for n < 64 is a huge shift amount and so also gives zero.
+// 16 bytes with byte `i` set to 1, given n = 8*i; any n >= 128 gives zeros.  Word w of the result
+// is 1 << (n - 32*w) under the clamping shift: for n below the word the subtraction wraps to a
+// huge amount, for n above it the amount is 32 or more, and both give zero.
 __device__ __forceinline__ uint4 onehot16_bits(uint32_t n) {
-    const uint64_t lo = shl64_clamped(1ull, n), hi = shl64_clamped(1ull, n - 64u);
-    return make_uint4((uint32_t)lo, (uint32_t)(lo >> 32), (uint32_t)hi, (uint32_t)(hi >> 32));
+    return make_uint4(shl32_clamped(1u, n), shl32_clamped(1u, n - 32u), shl32_clamped(1u, n - 64u),
+                      shl32_clamped(1u, n - 96u));
 }
 __device__ __forceinline__ uint4 onehot16(uint32_t i) { return onehot16_bits(i < 16u ? i * 8u : 128u); }
 

@@ -77,6 +77,10 @@ def test_config1_bert_base_ffn1(ctx):
     (33, 512, 16, 32, 256),    # widest index
     (70, 60, 32, 3, 5),        # odd v, odd CT: generic search path, gather only
     (50, 35, 16, 5, 7),
+    (130, 160, 64, 10, 16),    # hidden 2560 / 256 codebooks: v = 10
+    (65, 320, 32, 20, 16),     # hidden 5120 / 256 codebooks: v = 20
+    (33, 96, 16, 6, 16), (20, 192, 16, 12, 8), (9, 384, 16, 24, 16),
+    (17, 112, 16, 7, 16),      # v with no compile-time instance: run-time length path
     (256, 768, 768, 2, 16),    # BERT-base attention-out
 ])
 def test_shapes(ctx, M, K, N, v, CT):
