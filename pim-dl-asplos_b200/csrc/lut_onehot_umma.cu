@@ -49,6 +49,11 @@ constexpr uint32_t kFirstAgenWarp = 2;
 constexpr uint32_t kMaxThreads = (kFirstAgenWarp + 4 * kMaxAgenGroups + kEpiWarps) * 32;  // 704
 constexpr uint32_t kMaxStages = 8;
 constexpr uint32_t kStageWarpBytes = 32 * 128;           // epilogue transpose buffer per warp
+// One-hot table: row e (0..15) holds the 16 bytes "byte e = 1", row 16 holds zeros; a row is 128
+// bytes = eight copies, and lane l reads copy l % 8, so a 16-byte load is free of bank conflicts
+// whatever indices the lanes of a warp hold.
+constexpr uint32_t kOneHotRows = 17;
+constexpr uint32_t kOneHotTabBytes = kOneHotRows * 128;
 
 struct UmmaParams {
     LutArgs a;
@@ -116,7 +121,8 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
     unsigned char* s_a = smem;                                   // [S][SPS][16 KiB], 1024-aligned
     unsigned char* s_b = s_a + (size_t)S * kAStageBytes;         // [S][SPS][N_TILE*128], 1024-aligned
     unsigned char* s_stage = s_b + (size_t)S * kBStageBytes;     // [4][32][128] epilogue transpose
-    uint64_t* s_bar = reinterpret_cast<uint64_t*>(s_stage + kEpiWarps * kStageWarpBytes);
+    unsigned char* s_tab = s_stage + kEpiWarps * kStageWarpBytes;  // one-hot table, 128-byte aligned
+    uint64_t* s_bar = reinterpret_cast<uint64_t*>(s_tab + kOneHotTabBytes);
     uint32_t* s_misc = reinterpret_cast<uint32_t*>(s_bar + 2 * kMaxStages + 4);  // tmem base, abort, last
     volatile uint32_t* s_abort = s_misc + 1;
 
@@ -142,6 +148,10 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
         fence_barrier_init();
         tma_prefetch_desc(&lut_t_map);
     }
+    if (threadIdx.x >= 32 && threadIdx.x < 32 + kOneHotRows * 8) {
+        const uint32_t e = (threadIdx.x - 32) >> 3, copy = (threadIdx.x - 32) & 7u;
+        *reinterpret_cast<uint4*>(s_tab + e * 128 + copy * 16) = onehot16(e);
+    }
     __syncthreads();
     if (warp == 1) {
         tmem_alloc(smem_u32(s_misc), kTmemCols);
@@ -165,7 +175,7 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
                 const Item it = decode_item(p, item, N_TILE);
                 const uint32_t rounds = (it.nslab + SPS - 1) / SPS;
                 for (uint32_t rr = 0; rr < rounds; ++rr) {
-                    ok = mbar_wait(empty0 + 8 * s, ph ^ 1, s_abort);
+                    ok = mbar_wait<64>(empty0 + 8 * s, ph ^ 1, s_abort);
                     if (!ok) break;
                     const uint32_t valid = min(SPS, it.nslab - rr * SPS);
                     mbar_arrive_expect_tx(full0 + 8 * s, valid * kBBytes);
@@ -243,6 +253,7 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
         const uint32_t r = (warp & 3u) * 32 + lane;  // tile row == TMEM lane
         const uint32_t sw = r & 7u;
         const uint32_t CT = a.CT, lg = p.log2_ct;
+        const unsigned char* tab_lane = s_tab + (lane & 7u) * 16;
         // bytes of index one slab needs per row: 128 / CT codebooks (at least one byte)
         auto load_raw = [&](const uint8_t* row, uint32_t slab) -> uint4 {
             const uint8_t* q = row + ((slab * kSlabK) >> lg);
@@ -254,52 +265,85 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
             else v.x = __ldcg(q);
             return v;
         };
+        // With the operand in tensor memory a group takes kBatch consecutive slabs (one stage, or half
+        // of one) per turn: the fixed cost of a turn - the wait for a free stage, the fences, the
+        // arrival, the loop itself, a chain of latencies of well over a thousand cycles for a lone
+        // warp - is paid once per batch.  (In shared memory a stage is large, few are in flight, and
+        // one slab per turn keeps more groups busy.)
+        constexpr uint32_t kBatch = (A_TMEM && SPS % 2 == 0) ? 2u : 1u;
+        // Index bytes are fetched kPrefetch turns ahead: with the LUT tiles streaming through the same
+        // L2 a load takes a good part of a turn.
+        constexpr uint32_t kPrefetch = 2;
         uint32_t g = 0;  // slab counter of the CTA, items padded to whole rounds
         bool ok = true;
         for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
             const Item it = decode_item(p, item, N_TILE);
             const uint32_t padded = ((it.nslab + SPS - 1) / SPS) * SPS;
             const uint8_t* grow = a.idx + (size_t)min(it.m0 + r, a.M - 1) * a.CB;  // rows past M: masked in the epilogue
-            uint32_t i = (grp + kAgenGroups - (g % kAgenGroups)) % kAgenGroups;
+            // g and padded are multiples of SPS, hence of kBatch: batch number (g + i) / kBatch goes to
+            // group (that number) % groups
+            uint32_t i = kBatch * ((grp + kAgenGroups - ((g / kBatch) % kAgenGroups)) % kAgenGroups);
+            const uint32_t stride = kBatch * kAgenGroups;
             // round, stage and phase bit of slab g + i; advanced incrementally below
             uint32_t R = (g + i) / SPS, s = R % S, ph = (R / S) & 1;
-            uint4 raw_next = make_uint4(0, 0, 0, 0);
-            if (i < it.nslab) raw_next = load_raw(grow, it.slab_begin + i);
-            for (; i < padded && ok; i += kAgenGroups) {
-                const uint32_t slab = it.slab_begin + i;
-                const uint4 raw = raw_next;
-                if (i + kAgenGroups < it.nslab) raw_next = load_raw(grow, slab + kAgenGroups);
-                uint4 chunk[8];
-                if (lg == 4) {  // one codebook == one 16-byte chunk
-                    // indices are < 16, so 8*idx still fits its byte: shift all four at once
-                    const uint32_t n8[2] = {raw.x << 3, raw.y << 3};
+            uint4 raw_q[kPrefetch][kBatch];
 #pragma unroll
-                    for (uint32_t j = 0; j < 8; ++j) chunk[j] = onehot16_bits((n8[j >> 2] >> (8 * (j & 3))) & 0xFFu);
-                } else if (lg == 3) {  // two codebooks per chunk
-                    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+            for (uint32_t k = 0; k < kPrefetch; ++k)
 #pragma unroll
-                    for (uint32_t j = 0; j < 8; ++j) {
-                        const uint32_t two = (w[j >> 1] >> (16 * (j & 1))) & 0xFFFFu;
-                        const uint4 lo = onehot16(two & 7u), hi = onehot16(((two >> 8) & 7u) + 8u);
-                        chunk[j] = make_uint4(lo.x | hi.x, lo.y | hi.y, lo.z | hi.z, lo.w | hi.w);
-                    }
-                } else {  // a codebook spans CT/16 chunks
-#pragma unroll
-                    for (uint32_t j = 0; j < 8; ++j) {
-                        const uint32_t k0 = slab * kSlabK + 16 * j;
-                        const uint32_t ix = (raw.x >> (8 * (j >> (lg - 4)))) & 0xFFu;  // CT >= 128: always byte 0
-                        const uint32_t sub = (k0 & (CT - 1)) >> 4;
-                        chunk[j] = onehot16((ix >> 4) == sub ? (ix & 15u) : 16u);
-                    }
+                for (uint32_t b = 0; b < kBatch; ++b) {
+                    raw_q[k][b] = make_uint4(0, 0, 0, 0);
+                    if (i + k * stride + b < it.nslab) raw_q[k][b] = load_raw(grow, it.slab_begin + i + k * stride + b);
                 }
-                const uint32_t gg = g + i, h = gg % SPS;
+            for (; i < padded && ok; i += stride) {
+                uint4 raw[kBatch];
+#pragma unroll
+                for (uint32_t b = 0; b < kBatch; ++b) {
+                    raw[b] = raw_q[0][b];
+#pragma unroll
+                    for (uint32_t k = 0; k + 1 < kPrefetch; ++k) raw_q[k][b] = raw_q[k + 1][b];
+                    if (i + kPrefetch * stride + b < it.nslab)
+                        raw_q[kPrefetch - 1][b] = load_raw(grow, it.slab_begin + i + kPrefetch * stride + b);
+                }
+                const uint32_t gg = g + i, h0 = gg % SPS;
                 for (const uint32_t Rn = gg / SPS; R < Rn; ++R)
                     if (++s == S) { s = 0; ph ^= 1; }
-                uint32_t w_ok = 1;
-                if (lane == 0) w_ok = mbar_wait(empty0 + 8 * s, ph ^ 1, s_abort) ? 1u : 0u;
-                ok = __shfl_sync(0xffffffffu, w_ok, 0) != 0;
+                // the whole warp polls (one broadcast access), so it stays converged
+                ok = mbar_wait(empty0 + 8 * s, ph ^ 1, s_abort);
                 if (!ok) break;
-                if (i < it.nslab) {  // padding slabs of a last, partial round only arrive
+                if constexpr (A_TMEM) tc_fence_after_sync();
+#pragma unroll
+                for (uint32_t b = 0; b < kBatch; ++b) {
+                    if (i + b >= it.nslab) continue;  // padding slabs of a last, partial round only arrive
+                    const uint32_t slab = it.slab_begin + i + b, h = h0 + b;
+                    // Row of the one-hot table per 16-byte chunk, then one conflict-free 16-byte load each.
+                    // An index that is out of range for its chunk selects the all-zero row (the indices
+                    // may come from a caller, not only from the search kernel).
+                    uint4 chunk[8];
+                    if (lg == 4) {  // one codebook == one 16-byte chunk
+#pragma unroll
+                        for (uint32_t j = 0; j < 8; ++j) {
+                            const uint32_t ix = ((j < 4 ? raw[b].x : raw[b].y) >> (8 * (j & 3))) & 0xFFu;
+                            chunk[j] = *reinterpret_cast<const uint4*>(tab_lane + min(ix, 16u) * 128);
+                        }
+                    } else if (lg == 3) {  // two codebooks per chunk: low eight bytes, high eight bytes
+                        const uint32_t w[4] = {raw[b].x, raw[b].y, raw[b].z, raw[b].w};
+#pragma unroll
+                        for (uint32_t j = 0; j < 8; ++j) {
+                            const uint32_t two = (w[j >> 1] >> (16 * (j & 1))) & 0xFFFFu;
+                            const uint32_t i0 = two & 0xFFu, i1 = two >> 8;
+                            const uint4 lo = *reinterpret_cast<const uint4*>(tab_lane + (i0 < 8u ? i0 : 16u) * 128);
+                            const uint4 hi = *reinterpret_cast<const uint4*>(tab_lane + (i1 < 8u ? i1 + 8u : 16u) * 128);
+                            chunk[j] = make_uint4(lo.x | hi.x, lo.y | hi.y, lo.z | hi.z, lo.w | hi.w);
+                        }
+                    } else {  // a codebook spans CT/16 chunks
+#pragma unroll
+                        for (uint32_t j = 0; j < 8; ++j) {
+                            const uint32_t k0 = slab * kSlabK + 16 * j;
+                            const uint32_t ix = (raw[b].x >> (8 * (j >> (lg - 4)))) & 0xFFu;  // CT >= 128: always byte 0
+                            const uint32_t sub = (k0 & (CT - 1)) >> 4;
+                            chunk[j] = *reinterpret_cast<const uint4*>(tab_lane + ((ix >> 4) == sub ? (ix & 15u) : 16u) * 128);
+                        }
+                    }
                     if constexpr (A_TMEM) {
                         // the row goes to this warp's lane quadrant of tensor memory, K bytes in column order
                         uint32_t w[32];
@@ -307,20 +351,22 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
                         for (uint32_t j = 0; j < 8; ++j) {
                             w[4 * j + 0] = chunk[j].x; w[4 * j + 1] = chunk[j].y; w[4 * j + 2] = chunk[j].z; w[4 * j + 3] = chunk[j].w;
                         }
-                        tc_fence_after_sync();
                         tmem_st_32x32b_x32(tmem_base + (((warp & 3u) * 32u) << 16) + kATmemBase + (s * SPS + h) * 32, w);
-                        tmem_st_wait();
-                        tc_fence_before_sync();
                     } else {
                         unsigned char* row_ptr = s_a + (size_t)(s * SPS + h) * kABytes + r * kSlabK;
 #pragma unroll
                         for (uint32_t j = 0; j < 8; ++j)  // 128-byte swizzle: 16-byte chunk j of row r lands at j ^ (r & 7)
                             *reinterpret_cast<uint4*>(row_ptr + ((j ^ sw) << 4)) = chunk[j];
-                        fence_proxy_async_smem();
                     }
                 }
+                if constexpr (A_TMEM) {
+                    tmem_st_wait();
+                    tc_fence_before_sync();
+                } else {
+                    fence_proxy_async_smem();
+                }
                 __syncwarp();
-                if (lane == 0) mbar_arrive(full0 + 8 * s);
+                if (lane == 0) mbar_arrive_n(full0 + 8 * s, kBatch);
             }
             g += padded;
         }
@@ -346,7 +392,7 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
             };
             float4 b_next = load_bias(0);
             uint32_t w_ok = 1;
-            if (lane == 0) w_ok = (ok && mbar_wait(acc_full0 + 8 * ab, aph, s_abort)) ? 1u : 0u;
+            if (lane == 0) w_ok = (ok && mbar_wait<256>(acc_full0 + 8 * ab, aph, s_abort)) ? 1u : 0u;
             ok = __shfl_sync(0xffffffffu, w_ok, 0) != 0;
             if (ok) {
                 tc_fence_after_sync();
@@ -369,30 +415,55 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
                     __syncwarp();
                     const uint32_t n = it.n0 + c * 32 + ch * 4;
                     if (n < a.N) {  // N % 16 == 0: a 4-column group is in or out as a whole
+                        // One warp per scheduler is all that runs here, so the eight row passes are
+                        // written as straight-line code with their loads, conversions and stores
+                        // grouped: a pass-by-pass loop leaves every latency exposed.
+                        const uint32_t m_first = it.m0 + quad * 32 + rsub;  // row of pass 0; pass k is 4k rows further
 #pragma unroll
-                        for (uint32_t pass = 0; pass < 8; ++pass) {
-                            const uint32_t rr = pass * 4 + rsub;
-                            const uint32_t mm = it.m0 + quad * 32 + rr;
-                            if (mm >= a.M) continue;
-                            const int4 val = *reinterpret_cast<const int4*>(stg + rr * 128 + ((ch ^ (rr & 7u)) << 4));
+                        for (uint32_t half = 0; half < 2; ++half) {  // four passes at a time: registers
+                            int4 val[4];
+#pragma unroll
+                            for (uint32_t k = 0; k < 4; ++k) {
+                                const uint32_t rr = (half * 4 + k) * 4 + rsub;
+                                val[k] = *reinterpret_cast<const int4*>(stg + rr * 128 + ((ch ^ (rr & 7u)) << 4));
+                            }
+                            const uint32_t m_half = m_first + half * 16;
                             if (p.split > 1) {  // this slice's partial sums, plain row-contiguous stores
-                                __stcg(reinterpret_cast<int4*>(p.acc_scratch + ((size_t)it.z * a.M + mm) * a.N + n), val);
+#pragma unroll
+                                for (uint32_t k = 0; k < 4; ++k)
+                                    if (m_half + k * 4 < a.M)
+                                        __stcg(reinterpret_cast<int4*>(p.acc_scratch + ((size_t)it.z * a.M + m_half + k * 4) * a.N + n), val[k]);
                                 continue;
                             }
-                            float4 o;
-                            o.x = dequant_one(val.x, a.scale, lbcb, b4.x);
-                            o.y = dequant_one(val.y, a.scale, lbcb, b4.y);
-                            o.z = dequant_one(val.z, a.scale, lbcb, b4.z);
-                            o.w = dequant_one(val.w, a.scale, lbcb, b4.w);
-                            if (!a.layout.tiled) {
-                                *reinterpret_cast<float4*>(a.out + (size_t)mm * a.N + n) = o;
-                            } else {
-                                a.out[tiled_out_offset(mm, n + 0, a.layout)] = o.x;
-                                a.out[tiled_out_offset(mm, n + 1, a.layout)] = o.y;
-                                a.out[tiled_out_offset(mm, n + 2, a.layout)] = o.z;
-                                a.out[tiled_out_offset(mm, n + 3, a.layout)] = o.w;
+                            float4 o[4];
+#pragma unroll
+                            for (uint32_t k = 0; k < 4; ++k) {
+                                o[k].x = dequant_one(val[k].x, a.scale, lbcb, b4.x);
+                                o[k].y = dequant_one(val[k].y, a.scale, lbcb, b4.y);
+                                o[k].z = dequant_one(val[k].z, a.scale, lbcb, b4.z);
+                                o[k].w = dequant_one(val[k].w, a.scale, lbcb, b4.w);
                             }
-                            if (a.acc_out) *reinterpret_cast<int4*>(a.acc_out + (size_t)mm * a.N + n) = val;
+                            if (!a.layout.tiled) {
+                                float* orow = a.out + (size_t)m_half * a.N + n;
+#pragma unroll
+                                for (uint32_t k = 0; k < 4; ++k)
+                                    if (m_half + k * 4 < a.M) *reinterpret_cast<float4*>(orow + (size_t)k * 4 * a.N) = o[k];
+                            } else {
+                                for (uint32_t k = 0; k < 4; ++k) {
+                                    const uint32_t mm = m_half + k * 4;
+                                    if (mm >= a.M) continue;
+                                    a.out[tiled_out_offset(mm, n + 0, a.layout)] = o[k].x;
+                                    a.out[tiled_out_offset(mm, n + 1, a.layout)] = o[k].y;
+                                    a.out[tiled_out_offset(mm, n + 2, a.layout)] = o[k].z;
+                                    a.out[tiled_out_offset(mm, n + 3, a.layout)] = o[k].w;
+                                }
+                            }
+                            if (a.acc_out) {
+#pragma unroll
+                                for (uint32_t k = 0; k < 4; ++k)
+                                    if (m_half + k * 4 < a.M)
+                                        *reinterpret_cast<int4*>(a.acc_out + (size_t)(m_half + k * 4) * a.N + n) = val[k];
+                            }
                         }
                     }
                 }
@@ -481,7 +552,7 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
 
 size_t umma_smem_bytes(uint32_t n_tile, uint32_t stages, bool a_tmem, uint32_t sps) {
     return (size_t)stages * sps * ((a_tmem ? 0 : kABytes) + n_tile * kSlabK) + kEpiWarps * kStageWarpBytes +
-           (2 * kMaxStages + 4) * 8 + 16 + 1024;
+           kOneHotTabBytes + (2 * kMaxStages + 4) * 8 + 16 + 1024;
 }
 constexpr size_t kSmemLimit = 227 * 1024;
 
@@ -629,7 +700,11 @@ cudaError_t launch_umma(const LutArgs& a, const CUtensorMap& lut_t_map, const Um
     // A builder group may run at most one use of a stage ahead of the MMA warp (mbarrier
     // parity only tells two consecutive phases apart), which holds iff groups <= stages * slabs per stage.
     p.groups = plan.groups ? (plan.groups > kMaxAgenGroups ? kMaxAgenGroups : plan.groups) : 4;
-    if (p.groups > p.stages * sps) p.groups = p.stages * sps;
+    {   // a group holds two slabs per turn when the one-hot operand goes to tensor memory and a stage has an even number
+        const uint32_t batch = (a_tmem && sps % 2 == 0) ? 2u : 1u;
+        if (p.groups > p.stages * sps / batch) p.groups = p.stages * sps / batch;
+        if (p.groups == 0) p.groups = 1;
+    }
     if (split > 1 && (!acc_scratch || !tile_counters)) { *why = "tcgen05 variant: split > 1 needs scratch"; return cudaErrorInvalidValue; }
     const size_t smem = umma_smem_bytes(plan.n_tile, p.stages, a_tmem, sps);
     const uint64_t items = (uint64_t)p.tiles_m * p.tiles_n * split;

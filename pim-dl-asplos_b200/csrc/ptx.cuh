@@ -31,6 +31,10 @@ __device__ __forceinline__ void fence_barrier_init() {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// n arrivals at once (n >= 1)
+__device__ __forceinline__ void mbar_arrive_n(uint32_t bar, uint32_t n) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(n) : "memory");
+}
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
@@ -47,12 +51,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 // Bounded wait.  `abort_word` is a shared-memory word any role sets once something went
 // wrong; every waiter polls it so one failure releases the whole CTA.
+// kSleepNs > 0: back off between polls.  For roles whose waits are long by design (an epilogue
+// waiting out a whole main loop, a producer waiting for a free stage): their polling otherwise
+// competes for issue slots and for the shared-memory pipe with the warps on the critical path.
+template <uint32_t kSleepNs = 0>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_word) {
     if (mbar_try_wait(bar, parity)) return true;
     if (*abort_word) return false;
     for (uint32_t it = 0; it < kWaitLimit; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((it & 63u) == 63u && *abort_word) return false;
+        if constexpr (kSleepNs > 0) __nanosleep(kSleepNs);
     }
     *abort_word = 1u;
     return false;
