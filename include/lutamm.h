@@ -97,12 +97,12 @@ typedef struct lutamm_plan {
     uint32_t gather_cfg;      /* gather kernel tile configuration id (0 = default)        */
     uint32_t umma_n_tile;     /* tcgen05 N tile: 64, 128, 192 or 256 (0 = default)        */
     uint32_t umma_split;      /* tcgen05 split of the codebook axis across CTAs (0 = auto) */
-    uint32_t umma_stages;     /* tcgen05 pipeline depth (0 = as deep as fits)             */
+    uint32_t umma_stages;     /* tcgen05: LUT slabs in flight in shared memory (0 = as many as fit) */
     uint32_t umma_groups;     /* tcgen05 one-hot builder groups of 4 warps (0 = default)  */
     uint32_t umma_operand;    /* where the one-hot operand lives: 0 = default,
                                  1 = shared memory, 2 = tensor memory (TMEM)             */
-    uint32_t umma_sps;        /* tcgen05: 128-byte slabs of the codebook axis per pipeline
-                                 stage, 1, 2 or 4 (0 = default)                           */
+    uint32_t umma_sps;        /* tcgen05: 128-byte slabs of the codebook axis a one-hot builder
+                                 group takes per turn, 1 or 2 (0 = default; 4 is read as 2)  */
     uint32_t reserved;
 } lutamm_plan;
 

@@ -52,9 +52,9 @@ struct UmmaPlan {
     uint32_t n_tile;    // 64 / 128 / 256 (A in shared memory), 64 / 128 / 192 (A in tensor memory)
     uint32_t a_tmem;    // 1: the one-hot operand is written to tensor memory instead of shared memory
     uint32_t split;     // work items sharing one output tile along the codebook axis
-    uint32_t stages;    // 0 = as many as fit
+    uint32_t stages;    // LUT slabs in flight in shared memory (0 = as many as fit)
     uint32_t groups;    // one-hot builder groups of four warps (0 = default)
-    uint32_t sps;       // 128-byte slabs of the contraction axis per pipeline stage: 1, 2 (default) or 4
+    uint32_t sps;       // 128-byte slabs a one-hot builder group takes per turn: 1 or 2 (0 = by ring depth)
     uint32_t max_ctas;  // persistent grid size cap: the SM count
 };
 bool umma_supported(uint32_t CB, uint32_t CT, uint32_t N);

@@ -47,7 +47,9 @@ constexpr uint32_t kEpiWarps = 4;
 constexpr uint32_t kEpiThreads = kEpiWarps * 32;
 constexpr uint32_t kFirstAgenWarp = 2;
 constexpr uint32_t kMaxThreads = (kFirstAgenWarp + 4 * kMaxAgenGroups + kEpiWarps) * 32;  // 704
-constexpr uint32_t kMaxStages = 8;
+constexpr uint32_t kMaxASlots = 8;    // one-hot slabs in flight (tensor memory: 32 columns each)
+constexpr uint32_t kMaxBSlots = 16;   // LUT slabs in flight (shared memory)
+constexpr uint32_t kNumBarriers = 2 * kMaxASlots + 2 * kMaxBSlots + 4;
 constexpr uint32_t kStageWarpBytes = 32 * 128;           // epilogue transpose buffer per warp
 // One-hot table: row e (0..15) holds the 16 bytes "byte e = 1", row 16 holds zeros; a row is 128
 // bytes = eight copies, and lane l reads copy l % 8, so a 16-byte load is free of bank conflicts
@@ -60,7 +62,9 @@ struct UmmaParams {
     uint32_t slabs_total;    // ceil(CB*CT / 128)
     uint32_t slabs_per_item; // ceil(slabs_total / split)
     uint32_t split;
-    uint32_t stages;
+    uint32_t a_slots;        // ring of one-hot slabs (tensor memory or shared memory), a power of two
+    uint32_t a_slots_log2;
+    uint32_t b_slots;        // ring of LUT slabs (shared memory), at least a_slots
     uint32_t tiles_m, tiles_n;
     uint32_t log2_ct;
     uint32_t groups;         // A-builder groups (1..6)
@@ -112,22 +116,26 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
     // A slabs (32 columns = 128 bytes of K per row) behind them.
     constexpr uint32_t kTmemCols = A_TMEM ? 512u : (2 * N_TILE <= 32 ? 32u : 2 * N_TILE <= 64 ? 64u : 2 * N_TILE <= 128 ? 128u : 2 * N_TILE <= 256 ? 256u : 512u);
     constexpr uint32_t kATmemBase = 2 * N_TILE;
-    constexpr uint32_t kAStageBytes = A_TMEM ? 0u : SPS * kABytes;
-    constexpr uint32_t kBStageBytes = SPS * kBBytes;
+    constexpr uint32_t kASlotBytes = A_TMEM ? 0u : kABytes;
+    constexpr uint32_t kUnroll = N_TILE >= 192 ? 2u : 4u;  // slabs per turn of the MMA warp's loop
 
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-    const uint32_t S = p.stages;
-    unsigned char* s_a = smem;                                   // [S][SPS][16 KiB], 1024-aligned
-    unsigned char* s_b = s_a + (size_t)S * kAStageBytes;         // [S][SPS][N_TILE*128], 1024-aligned
-    unsigned char* s_stage = s_b + (size_t)S * kBStageBytes;     // [4][32][128] epilogue transpose
+    // Two rings, one slab (128 bytes of the contraction axis) per slot.  The LUT ring is as deep as
+    // shared memory allows: a TMA tile takes on the order of a microsecond to arrive, several slab
+    // times, and it is the number of tiles in flight that hides it.  The one-hot ring is bounded by
+    // tensor memory (what the two accumulators leave) or, in shared memory, by what the LUT ring leaves.
+    const uint32_t SA = p.a_slots, SB = p.b_slots;
+    unsigned char* s_a = smem;                                   // [SA][16 KiB], 1024-aligned (A in shared memory only)
+    unsigned char* s_b = s_a + (size_t)SA * kASlotBytes;         // [SB][N_TILE*128], 1024-aligned
+    unsigned char* s_stage = s_b + (size_t)SB * kBBytes;         // [4][32][128] epilogue transpose
     unsigned char* s_tab = s_stage + kEpiWarps * kStageWarpBytes;  // one-hot table, 128-byte aligned
     uint64_t* s_bar = reinterpret_cast<uint64_t*>(s_tab + kOneHotTabBytes);
-    uint32_t* s_misc = reinterpret_cast<uint32_t*>(s_bar + 2 * kMaxStages + 4);  // tmem base, abort, last
+    uint32_t* s_misc = reinterpret_cast<uint32_t*>(s_bar + kNumBarriers);  // tmem base, abort, last
     volatile uint32_t* s_abort = s_misc + 1;
 
-    const uint32_t full0 = smem_u32(s_bar), empty0 = smem_u32(s_bar + kMaxStages),
-                   acc_full0 = smem_u32(s_bar + 2 * kMaxStages), acc_empty0 = smem_u32(s_bar + 2 * kMaxStages + 2);
+    const uint32_t a_full0 = smem_u32(s_bar), a_empty0 = a_full0 + 8 * kMaxASlots, b_full0 = a_empty0 + 8 * kMaxASlots,
+                   b_empty0 = b_full0 + 8 * kMaxBSlots, acc_full0 = b_empty0 + 8 * kMaxBSlots, acc_empty0 = acc_full0 + 16;
 
     const LutArgs& a = p.a;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -137,9 +145,13 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
 
     if (threadIdx.x == 0) {
         s_misc[0] = 0; s_misc[1] = 0; s_misc[2] = 0;
-        for (uint32_t s = 0; s < S; ++s) {
-            mbar_init(full0 + 8 * s, SPS * 4 + 1);  // four builder warps per slab of the stage + the TMA
-            mbar_init(empty0 + 8 * s, 1);            // tcgen05.commit
+        for (uint32_t k = 0; k < SA; ++k) {
+            mbar_init(a_full0 + 8 * k, 4);   // the four builder warps of the group that owns the slab
+            mbar_init(a_empty0 + 8 * k, 1);  // tcgen05.commit
+        }
+        for (uint32_t j = 0; j < SB; ++j) {
+            mbar_init(b_full0 + 8 * j, 1);   // the producer's arrive.expect_tx; the TMA completes the bytes
+            mbar_init(b_empty0 + 8 * j, 1);  // tcgen05.commit
         }
         for (uint32_t b = 0; b < 2; ++b) {
             mbar_init(acc_full0 + 8 * b, 1);           // tcgen05.commit
@@ -162,78 +174,96 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
     tc_fence_after_sync();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(s_misc);
 
-    // A "round" is one pipeline stage's worth of the contraction axis: SPS slabs of 128 bytes,
-    // 4*SPS tcgen05.mma between one wait and one commit.  The commit/wait round trip costs a
-    // few hundred cycles on the issuing thread whatever the stage holds, so a stage has to
-    // hold enough math to hide it.
     if (warp == 0) {
         // ---------------- TMA producer (the LUT never depends on the preceding kernel)
         if (lane == 0) {
-            uint32_t s = 0, ph = 0;  // stage and phase bit of the current round
+            uint32_t j = 0, ph = 0;  // LUT slot and the phase bit of its current use
             bool ok = true;
             for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
                 const Item it = decode_item(p, item, N_TILE);
-                const uint32_t rounds = (it.nslab + SPS - 1) / SPS;
-                for (uint32_t rr = 0; rr < rounds; ++rr) {
-                    ok = mbar_wait<64>(empty0 + 8 * s, ph ^ 1, s_abort);
+                for (uint32_t i = 0; i < it.nslab; ++i) {
+                    ok = mbar_wait<32>(b_empty0 + 8 * j, ph ^ 1, s_abort);
                     if (!ok) break;
-                    const uint32_t valid = min(SPS, it.nslab - rr * SPS);
-                    mbar_arrive_expect_tx(full0 + 8 * s, valid * kBBytes);
-                    for (uint32_t h = 0; h < valid; ++h)
-                        tma_load_2d(smem_u32(s_b + (size_t)(s * SPS + h) * kBBytes), &lut_t_map, full0 + 8 * s,
-                                    (int32_t)((it.slab_begin + rr * SPS + h) * kSlabK), (int32_t)it.n0);
-                    if (++s == S) { s = 0; ph ^= 1; }
+                    mbar_arrive_expect_tx(b_full0 + 8 * j, kBBytes);
+                    tma_load_2d(smem_u32(s_b + (size_t)j * kBBytes), &lut_t_map, b_full0 + 8 * j,
+                                (int32_t)((it.slab_begin + i) * kSlabK), (int32_t)it.n0);
+                    if (++j == SB) { j = 0; ph ^= 1; }
                 }
             }
         }
         __syncwarp();
     } else if (warp == 1) {
         // ---------------- MMA issuer: the whole warp walks the loop converged (waits and
-        // descriptor arithmetic stay warp-uniform), one elected lane issues.
+        // descriptor arithmetic stay warp-uniform; a lone lane running the loop measured 20 %
+        // slower), one elected lane issues.  kUnroll slabs per turn: four tcgen05.mma (32 bytes of
+        // K each) per slab, then one commit per ring and slab hands the slots back.
         {
-            uint32_t s = 0, ph = 0, t = 0;
+            uint32_t k = 0, pa = 0, j = 0, pb = 0, t = 0;
             bool ok = true;
             const uint32_t b_lo0 = (uint32_t)umma_desc_k_sw128(smem_u32(s_b));
             const uint32_t a_lo0 = (uint32_t)umma_desc_k_sw128(smem_u32(s_a));
             const uint32_t desc_hi = (uint32_t)(umma_desc_k_sw128(0) >> 32);
             for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++t) {
                 const Item it = decode_item(p, item, N_TILE);
-                const uint32_t rounds = (it.nslab + SPS - 1) / SPS;
                 const uint32_t ab = t & 1, aph = (t >> 1) & 1;
                 ok = mbar_wait(acc_empty0 + 8 * ab, aph ^ 1, s_abort);  // epilogue drained this buffer
                 if (!ok) break;
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + ab * N_TILE;
-                for (uint32_t rr = 0; rr < rounds; ++rr) {
-                    ok = mbar_wait(full0 + 8 * s, ph, s_abort);
+                // The fixed cost of a turn of this loop (fence, election, re-convergence, the loop
+                // itself: several hundred cycles for a lone warp) exceeds what one slab's four MMAs
+                // take to execute, so a turn covers kUnroll slabs.
+                for (uint32_t i = 0; i < it.nslab; i += kUnroll) {
+                    const uint32_t nu = min(kUnroll, it.nslab - i);
+                    uint32_t ks[kUnroll], js[kUnroll], pas[kUnroll], pbs[kUnroll];
+#pragma unroll
+                    for (uint32_t u = 0; u < kUnroll; ++u) {
+                        ks[u] = k; js[u] = j; pas[u] = pa; pbs[u] = pb;
+                        if (u < nu) {
+                            if (++k == SA) { k = 0; pa ^= 1; }
+                            if (++j == SB) { j = 0; pb ^= 1; }
+                        }
+                    }
+                    // all of the turn's slots at once (slots past the turn's last slab repeat slab 0's)
+                    bool ready = true;
+#pragma unroll
+                    for (uint32_t u = 0; u < kUnroll; u += 2) {
+                        const uint32_t u1 = u + 1 < nu ? u + 1 : 0, u0 = u < nu ? u : 0;
+                        ready = mbar_test4(b_full0 + 8 * js[u0], pbs[u0], a_full0 + 8 * ks[u0], pas[u0],
+                                           b_full0 + 8 * js[u1], pbs[u1], a_full0 + 8 * ks[u1], pas[u1]) && ready;
+                    }
+                    if (!ready) {
+#pragma unroll
+                        for (uint32_t u = 0; u < kUnroll; ++u)
+                            if (u < nu)
+                                ok = ok && mbar_wait(b_full0 + 8 * js[u], pbs[u], s_abort) && mbar_wait(a_full0 + 8 * ks[u], pas[u], s_abort);
+                    }
                     if (!ok) break;
                     tc_fence_after_sync();
-                    const uint32_t valid = min(SPS, it.nslab - rr * SPS);
                     if (elect_one()) {
 #pragma unroll
-                        for (uint32_t h = 0; h < SPS; ++h) {
-                            if (h < valid) {
-                                // descriptors differ from the first slab's only in the 16-byte-unit address field
-                                const uint32_t b_lo = b_lo0 + (s * SPS + h) * (kBBytes >> 4);
-                                if constexpr (A_TMEM) {
-                                    const uint32_t ta = tmem_base + kATmemBase + (s * SPS + h) * 32;
+                        for (uint32_t u = 0; u < kUnroll; ++u) {
+                            if (u >= nu) continue;
+                            // descriptors differ from slot 0's only in the 16-byte-unit address field
+                            const uint32_t b_lo = b_lo0 + js[u] * (kBBytes >> 4);
+                            if constexpr (A_TMEM) {
+                                const uint32_t ta = tmem_base + kATmemBase + ks[u] * 32;
 #pragma unroll
-                                    for (uint32_t kk = 0; kk < kSlabK / 32; ++kk)  // 32 bytes of K = 8 TMEM columns of A
-                                        umma_i8_ts(d_tmem, ta + 8 * kk, ((uint64_t)desc_hi << 32) | (b_lo + 2 * kk), kIdesc,
-                                                   (rr | h | kk) != 0 ? 1u : 0u);
-                                } else {
-                                    const uint32_t a_lo = a_lo0 + (s * SPS + h) * (kABytes >> 4);
+                                for (uint32_t kk = 0; kk < kSlabK / 32; ++kk)  // 32 bytes of K = 8 TMEM columns of A
+                                    umma_i8_ts(d_tmem, ta + 8 * kk, ((uint64_t)desc_hi << 32) | (b_lo + 2 * kk), kIdesc,
+                                               (i | u | kk) != 0 ? 1u : 0u);
+                            } else {
+                                const uint32_t a_lo = a_lo0 + ks[u] * (kABytes >> 4);
 #pragma unroll
-                                    for (uint32_t kk = 0; kk < kSlabK / 32; ++kk)  // 32 bytes of K per instruction
-                                        umma_i8(d_tmem, ((uint64_t)desc_hi << 32) | (a_lo + 2 * kk),
-                                                ((uint64_t)desc_hi << 32) | (b_lo + 2 * kk), kIdesc, (rr | h | kk) != 0 ? 1u : 0u);
-                                }
+                                for (uint32_t kk = 0; kk < kSlabK / 32; ++kk)  // 32 bytes of K per instruction
+                                    umma_i8(d_tmem, ((uint64_t)desc_hi << 32) | (a_lo + 2 * kk),
+                                            ((uint64_t)desc_hi << 32) | (b_lo + 2 * kk), kIdesc, (i | u | kk) != 0 ? 1u : 0u);
                             }
+                            umma_commit(a_empty0 + 8 * ks[u]);  // each slot is free once these MMAs have read it
+                            umma_commit(b_empty0 + 8 * js[u]);
                         }
-                        umma_commit(empty0 + 8 * s);  // frees the stage once these MMAs have read it
                     }
                     __syncwarp();
-                    if (++s == S) { s = 0; ph ^= 1; }
                 }
                 if (ok && elect_one()) umma_commit(acc_full0 + 8 * ab);
                 __syncwarp();
@@ -265,27 +295,22 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
             else v.x = __ldcg(q);
             return v;
         };
-        // With the operand in tensor memory a group takes kBatch consecutive slabs (one stage, or half
-        // of one) per turn: the fixed cost of a turn - the wait for a free stage, the fences, the
-        // arrival, the loop itself, a chain of latencies of well over a thousand cycles for a lone
-        // warp - is paid once per batch.  (In shared memory a stage is large, few are in flight, and
-        // one slab per turn keeps more groups busy.)
-        constexpr uint32_t kBatch = (A_TMEM && SPS % 2 == 0) ? 2u : 1u;
+        // A group takes SPS consecutive slabs per turn: the fixed cost of a turn - the fences, the
+        // arrival, the loop itself, a chain of latencies of many hundred cycles for a lone warp - is
+        // then paid once per batch.  Batch q of the CTA's sequence goes to group q % groups; slab x of
+        // the sequence uses one-hot slot x % SA (SA is a power of two).
+        constexpr uint32_t kBatch = SPS;
         // Index bytes are fetched kPrefetch turns ahead: with the LUT tiles streaming through the same
         // L2 a load takes a good part of a turn.
         constexpr uint32_t kPrefetch = 2;
-        uint32_t g = 0;  // slab counter of the CTA, items padded to whole rounds
+        const uint32_t sa_mask = SA - 1, sa_log2 = p.a_slots_log2;
+        uint32_t ga = 0, qb = 0;  // slabs and batches of the CTA before the current item
         bool ok = true;
         for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
             const Item it = decode_item(p, item, N_TILE);
-            const uint32_t padded = ((it.nslab + SPS - 1) / SPS) * SPS;
             const uint8_t* grow = a.idx + (size_t)min(it.m0 + r, a.M - 1) * a.CB;  // rows past M: masked in the epilogue
-            // g and padded are multiples of SPS, hence of kBatch: batch number (g + i) / kBatch goes to
-            // group (that number) % groups
-            uint32_t i = kBatch * ((grp + kAgenGroups - ((g / kBatch) % kAgenGroups)) % kAgenGroups);
+            uint32_t i = kBatch * ((grp + kAgenGroups - (qb % kAgenGroups)) % kAgenGroups);  // first slab of the turn
             const uint32_t stride = kBatch * kAgenGroups;
-            // round, stage and phase bit of slab g + i; advanced incrementally below
-            uint32_t R = (g + i) / SPS, s = R % S, ph = (R / S) & 1;
             uint4 raw_q[kPrefetch][kBatch];
 #pragma unroll
             for (uint32_t k = 0; k < kPrefetch; ++k)
@@ -294,7 +319,7 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
                     raw_q[k][b] = make_uint4(0, 0, 0, 0);
                     if (i + k * stride + b < it.nslab) raw_q[k][b] = load_raw(grow, it.slab_begin + i + k * stride + b);
                 }
-            for (; i < padded && ok; i += stride) {
+            for (; i < it.nslab && ok; i += stride) {
                 uint4 raw[kBatch];
 #pragma unroll
                 for (uint32_t b = 0; b < kBatch; ++b) {
@@ -304,17 +329,15 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
                     if (i + kPrefetch * stride + b < it.nslab)
                         raw_q[kPrefetch - 1][b] = load_raw(grow, it.slab_begin + i + kPrefetch * stride + b);
                 }
-                const uint32_t gg = g + i, h0 = gg % SPS;
-                for (const uint32_t Rn = gg / SPS; R < Rn; ++R)
-                    if (++s == S) { s = 0; ph ^= 1; }
-                // the whole warp polls (one broadcast access), so it stays converged
-                ok = mbar_wait(empty0 + 8 * s, ph ^ 1, s_abort);
-                if (!ok) break;
-                if constexpr (A_TMEM) tc_fence_after_sync();
 #pragma unroll
                 for (uint32_t b = 0; b < kBatch; ++b) {
-                    if (i + b >= it.nslab) continue;  // padding slabs of a last, partial round only arrive
-                    const uint32_t slab = it.slab_begin + i + b, h = h0 + b;
+                    if (i + b >= it.nslab) continue;  // an odd last batch
+                    const uint32_t slab = it.slab_begin + i + b;
+                    const uint32_t x = ga + i + b, k = x & sa_mask, pa = (x >> sa_log2) & 1u;
+                    // the whole warp polls (one broadcast access), so it stays converged
+                    ok = ok && mbar_wait(a_empty0 + 8 * k, pa ^ 1, s_abort);
+                    if (!ok) continue;
+                    if constexpr (A_TMEM) tc_fence_after_sync();
                     // Row of the one-hot table per 16-byte chunk, then one conflict-free 16-byte load each.
                     // An index that is out of range for its chunk selects the all-zero row (the indices
                     // may come from a caller, not only from the search kernel).
@@ -351,9 +374,9 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
                         for (uint32_t j = 0; j < 8; ++j) {
                             w[4 * j + 0] = chunk[j].x; w[4 * j + 1] = chunk[j].y; w[4 * j + 2] = chunk[j].z; w[4 * j + 3] = chunk[j].w;
                         }
-                        tmem_st_32x32b_x32(tmem_base + (((warp & 3u) * 32u) << 16) + kATmemBase + (s * SPS + h) * 32, w);
+                        tmem_st_32x32b_x32(tmem_base + (((warp & 3u) * 32u) << 16) + kATmemBase + k * 32, w);
                     } else {
-                        unsigned char* row_ptr = s_a + (size_t)(s * SPS + h) * kABytes + r * kSlabK;
+                        unsigned char* row_ptr = s_a + (size_t)k * kABytes + r * kSlabK;
 #pragma unroll
                         for (uint32_t j = 0; j < 8; ++j)  // 128-byte swizzle: 16-byte chunk j of row r lands at j ^ (r & 7)
                             *reinterpret_cast<uint4*>(row_ptr + ((j ^ sw) << 4)) = chunk[j];
@@ -366,9 +389,14 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
                     fence_proxy_async_smem();
                 }
                 __syncwarp();
-                if (lane == 0) mbar_arrive_n(full0 + 8 * s, kBatch);
+                if (lane == 0 && ok) {
+#pragma unroll
+                    for (uint32_t b = 0; b < kBatch; ++b)
+                        if (i + b < it.nslab) mbar_arrive(a_full0 + 8 * ((ga + i + b) & sa_mask));
+                }
             }
-            g += padded;
+            ga += it.nslab;
+            qb += (it.nslab + kBatch - 1) / kBatch;
         }
     } else {
         // ---------------- epilogue: four warps, each on the TMEM lane quadrant (warp % 4) it may read
@@ -550,9 +578,9 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
     }
 }
 
-size_t umma_smem_bytes(uint32_t n_tile, uint32_t stages, bool a_tmem, uint32_t sps) {
-    return (size_t)stages * sps * ((a_tmem ? 0 : kABytes) + n_tile * kSlabK) + kEpiWarps * kStageWarpBytes +
-           kOneHotTabBytes + (2 * kMaxStages + 4) * 8 + 16 + 1024;
+size_t umma_smem_bytes(uint32_t n_tile, uint32_t a_slots, uint32_t b_slots, bool a_tmem) {
+    return (size_t)(a_tmem ? 0 : a_slots) * kABytes + (size_t)b_slots * n_tile * kSlabK + kEpiWarps * kStageWarpBytes +
+           kOneHotTabBytes + kNumBarriers * 8 + 16 + 1024;
 }
 constexpr size_t kSmemLimit = 227 * 1024;
 
@@ -574,15 +602,23 @@ cudaError_t run(const CUtensorMap& map, const UmmaParams& p, uint32_t grid, size
     return cudaLaunchKernelEx(&cfg, k, map, p);
 }
 
-// A in tensor memory: 512 columns hold two accumulators and the A ring, 32 columns a slab.
-uint32_t max_stages(uint32_t n_tile, bool a_tmem, uint32_t sps) {
-    uint32_t st = kMaxStages;
+// Ring depths.  One-hot slots: a power of two (the builders address them by mask); in tensor memory
+// what the two accumulators leave of the 512 columns, 32 columns a slab; in shared memory as many as
+// leave the LUT ring at least as deep.  LUT slots: whatever shared memory still holds.
+void ring_depths(uint32_t n_tile, bool a_tmem, uint32_t want_b, uint32_t* a_slots, uint32_t* b_slots) {
+    uint32_t sa = kMaxASlots;
     if (a_tmem) {
-        const uint32_t room = (512u - 2 * n_tile) / (32u * sps);
-        if (st > room) st = room;
+        const uint32_t room = (512u - 2 * n_tile) / 32u;
+        while (sa > room) sa >>= 1;
+    } else {
+        while (sa > 1 && umma_smem_bytes(n_tile, sa, sa, false) > kSmemLimit) sa >>= 1;
     }
-    while (st > 1 && umma_smem_bytes(n_tile, st, a_tmem, sps) > kSmemLimit) --st;
-    return st;
+    uint32_t sb = kMaxBSlots;
+    while (sb > sa && umma_smem_bytes(n_tile, sa, sb, a_tmem) > kSmemLimit) --sb;
+    if (want_b && want_b < sb) sb = want_b < 2 ? 2 : want_b;
+    if (sa > sb) sa = sb >= 8 ? 8 : sb >= 4 ? 4 : sb >= 2 ? 2 : 1;
+    *a_slots = sa;
+    *b_slots = sb;
 }
 bool tile_ok(uint32_t n_tile, bool a_tmem) {
     if (a_tmem) return n_tile == 64 || n_tile == 128 || n_tile == 192;
@@ -631,7 +667,7 @@ void umma_default_plan(uint32_t M, uint32_t CB, uint32_t CT, uint32_t N, int sm_
     if (operand == 0 && n_tile == 0) {
         if (N >= 256 && slabs >= 128 && tiles_for(256) >= 2u * (uint32_t)sm_count) { a_tmem = false; n_tile = 256; }
         else if (N >= 192 && tiles_for(192) >= (uint32_t)sm_count) { a_tmem = true; n_tile = 192; }
-        else { a_tmem = true; n_tile = N > 64 ? 128 : 64; if (!sps) sps = 4; }
+        else { a_tmem = true; n_tile = N > 64 ? 128 : 64; }
     } else if (operand == 0) {
         a_tmem = n_tile != 256;
     } else {
@@ -643,7 +679,7 @@ void umma_default_plan(uint32_t M, uint32_t CB, uint32_t CT, uint32_t N, int sm_
     p->split = umma_auto_split(M, CB, CT, N, n_tile, sm_count);
     p->stages = 0;
     p->groups = 0;
-    p->sps = sps ? sps : 2;
+    p->sps = sps;  // 0: chosen at launch from the ring depth
     p->max_ctas = (uint32_t)sm_count;
 }
 
@@ -684,12 +720,13 @@ cudaError_t launch_umma(const LutArgs& a, const CUtensorMap& lut_t_map, const Um
     p.slabs_per_item = (p.slabs_total + split - 1) / split;
     split = (p.slabs_total + p.slabs_per_item - 1) / p.slabs_per_item;  // no empty slices
     p.split = split;
-    const uint32_t sps = plan.sps == 4 ? 4u : (plan.sps == 1 ? 1u : 2u);
-    const uint32_t st_max = max_stages(plan.n_tile, a_tmem, sps);
-    if (st_max < 2) { *why = "tcgen05 variant: this tile / slabs-per-stage combination leaves room for fewer than two stages"; return cudaErrorInvalidValue; }
-    p.stages = plan.stages ? plan.stages : (st_max > 4 ? 4u : st_max);
-    if (p.stages > st_max) p.stages = st_max;
-    if (p.stages < 2) p.stages = 2;
+    ring_depths(plan.n_tile, a_tmem, plan.stages, &p.a_slots, &p.b_slots);
+    if (p.a_slots < 2 || p.b_slots < 2) { *why = "tcgen05 variant: this tile leaves room for fewer than two slabs in flight"; return cudaErrorInvalidValue; }
+    p.a_slots_log2 = 0;
+    while ((1u << p.a_slots_log2) < p.a_slots) ++p.a_slots_log2;
+    // slabs a builder group takes per turn
+    uint32_t sps = plan.sps == 1 ? 1u : (plan.sps >= 2 ? 2u : (p.a_slots >= 8 ? 2u : 1u));
+    if (sps > p.a_slots / 2) sps = 1;
     p.tiles_m = (a.M + kMTile - 1) / kMTile;
     p.tiles_n = (a.N + plan.n_tile - 1) / plan.n_tile;
     p.log2_ct = 0;
@@ -697,34 +734,32 @@ cudaError_t launch_umma(const LutArgs& a, const CUtensorMap& lut_t_map, const Um
     p.acc_scratch = acc_scratch;
     p.tile_counters = tile_counters;
     p.dev_err = dev_err;
-    // A builder group may run at most one use of a stage ahead of the MMA warp (mbarrier
-    // parity only tells two consecutive phases apart), which holds iff groups <= stages * slabs per stage.
+    // A builder group may run at most one use of a slot ahead of the MMA warp (mbarrier parity only
+    // tells two consecutive phases apart), which holds iff groups * slabs per turn <= one-hot slots.
     p.groups = plan.groups ? (plan.groups > kMaxAgenGroups ? kMaxAgenGroups : plan.groups) : 4;
-    {   // a group holds two slabs per turn when the one-hot operand goes to tensor memory and a stage has an even number
-        const uint32_t batch = (a_tmem && sps % 2 == 0) ? 2u : 1u;
-        if (p.groups > p.stages * sps / batch) p.groups = p.stages * sps / batch;
-        if (p.groups == 0) p.groups = 1;
-    }
+    if (p.groups > p.a_slots / sps) p.groups = p.a_slots / sps;
+    if (p.groups == 0) p.groups = 1;
     if (split > 1 && (!acc_scratch || !tile_counters)) { *why = "tcgen05 variant: split > 1 needs scratch"; return cudaErrorInvalidValue; }
-    const size_t smem = umma_smem_bytes(plan.n_tile, p.stages, a_tmem, sps);
+    const size_t smem = umma_smem_bytes(plan.n_tile, p.a_slots, p.b_slots, a_tmem);
     const uint64_t items = (uint64_t)p.tiles_m * p.tiles_n * split;
     const uint32_t cap = plan.max_ctas ? plan.max_ctas : 148u;
     const uint32_t grid = (uint32_t)(items < cap ? items : cap);
 #define LUTAMM_UMMA_CASE(NT, TM, SP) \
     if (plan.n_tile == NT && a_tmem == TM && sps == SP) return run<NT, TM, SP>(lut_t_map, p, grid, smem, s);
+    LUTAMM_UMMA_CASE(64, true, 1)
     LUTAMM_UMMA_CASE(64, true, 2)
+    LUTAMM_UMMA_CASE(128, true, 1)
     LUTAMM_UMMA_CASE(128, true, 2)
-    LUTAMM_UMMA_CASE(192, true, 2)
-    LUTAMM_UMMA_CASE(128, true, 4)
-    LUTAMM_UMMA_CASE(64, true, 4)
     LUTAMM_UMMA_CASE(192, true, 1)
+    LUTAMM_UMMA_CASE(192, true, 2)
+    LUTAMM_UMMA_CASE(64, false, 1)
     LUTAMM_UMMA_CASE(64, false, 2)
+    LUTAMM_UMMA_CASE(128, false, 1)
     LUTAMM_UMMA_CASE(128, false, 2)
-    LUTAMM_UMMA_CASE(256, false, 2)
     LUTAMM_UMMA_CASE(256, false, 1)
-    LUTAMM_UMMA_CASE(128, false, 4)
+    LUTAMM_UMMA_CASE(256, false, 2)
 #undef LUTAMM_UMMA_CASE
-    *why = "tcgen05 variant: this tile / operand / slabs-per-stage combination is not built";
+    *why = "tcgen05 variant: this tile / operand / slabs-per-turn combination is not built";
     return cudaErrorInvalidValue;
 }
 

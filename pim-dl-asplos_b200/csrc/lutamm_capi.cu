@@ -697,7 +697,7 @@ int lutamm_tune(lutamm_ctx* c, int layer_id, uint32_t M, lutamm_plan* best_out) 
     if (umma_supported(L->CB, L->CT, L->N)) {
         const uint32_t slabs = (uint32_t)(((uint64_t)L->CB * L->CT + 127) / 128);
         struct Cand { uint32_t operand, n_tile, sps; };
-        for (const Cand& cd : {Cand{1, 256, 2}, Cand{2, 192, 2}, Cand{2, 128, 4}, Cand{2, 128, 2}, Cand{1, 128, 2}}) {
+        for (const Cand& cd : {Cand{1, 256, 1}, Cand{2, 192, 1}, Cand{2, 128, 2}, Cand{2, 128, 1}, Cand{1, 128, 1}}) {
             if (cd.n_tile > 128 && L->N < cd.n_tile) continue;
             const uint32_t tiles = ((M + 127) / 128) * ((L->N + cd.n_tile - 1) / cd.n_tile);
             std::vector<uint32_t> splits = {1};
