@@ -117,7 +117,6 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
     constexpr uint32_t kTmemCols = A_TMEM ? 512u : (2 * N_TILE <= 32 ? 32u : 2 * N_TILE <= 64 ? 64u : 2 * N_TILE <= 128 ? 128u : 2 * N_TILE <= 256 ? 256u : 512u);
     constexpr uint32_t kATmemBase = 2 * N_TILE;
     constexpr uint32_t kASlotBytes = A_TMEM ? 0u : kABytes;
-    constexpr uint32_t kUnroll = N_TILE >= 192 ? 2u : 4u;  // slabs per turn of the MMA warp's loop
 
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -195,8 +194,9 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
     } else if (warp == 1) {
         // ---------------- MMA issuer: the whole warp walks the loop converged (waits and
         // descriptor arithmetic stay warp-uniform; a lone lane running the loop measured 20 %
-        // slower), one elected lane issues.  kUnroll slabs per turn: four tcgen05.mma (32 bytes of
-        // K each) per slab, then one commit per ring and slab hands the slots back.
+        // slower), one elected lane issues.  Per slab: four tcgen05.mma (32 bytes of K each), then
+        // one commit per ring hands the two slots back.  (Turns of two or four slabs measured
+        // slower: the one-hot ring is too shallow to have that many slabs ready at once.)
         {
             uint32_t k = 0, pa = 0, j = 0, pb = 0, t = 0;
             bool ok = true;
@@ -210,60 +210,43 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
                 if (!ok) break;
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + ab * N_TILE;
-                // The fixed cost of a turn of this loop (fence, election, re-convergence, the loop
-                // itself: several hundred cycles for a lone warp) exceeds what one slab's four MMAs
-                // take to execute, so a turn covers kUnroll slabs.
-                for (uint32_t i = 0; i < it.nslab; i += kUnroll) {
-                    const uint32_t nu = min(kUnroll, it.nslab - i);
-                    uint32_t ks[kUnroll], js[kUnroll], pas[kUnroll], pbs[kUnroll];
-#pragma unroll
-                    for (uint32_t u = 0; u < kUnroll; ++u) {
-                        ks[u] = k; js[u] = j; pas[u] = pa; pbs[u] = pb;
-                        if (u < nu) {
-                            if (++k == SA) { k = 0; pa ^= 1; }
-                            if (++j == SB) { j = 0; pb ^= 1; }
-                        }
-                    }
-                    // all of the turn's slots at once (slots past the turn's last slab repeat slab 0's)
-                    bool ready = true;
-#pragma unroll
-                    for (uint32_t u = 0; u < kUnroll; u += 2) {
-                        const uint32_t u1 = u + 1 < nu ? u + 1 : 0, u0 = u < nu ? u : 0;
-                        ready = mbar_test4(b_full0 + 8 * js[u0], pbs[u0], a_full0 + 8 * ks[u0], pas[u0],
-                                           b_full0 + 8 * js[u1], pbs[u1], a_full0 + 8 * ks[u1], pas[u1]) && ready;
-                    }
+                // Whether slab i's two slots are full is asked while slab i-1 is being issued: a barrier
+                // query is a round trip of the order of a hundred cycles, and two of them in front of
+                // every slab's instructions cost more than the slab's four MMAs take to execute.
+                bool ready = mbar_test2(b_full0 + 8 * j, pb, a_full0 + 8 * k, pa);
+                for (uint32_t i = 0; i < it.nslab; ++i) {
                     if (!ready) {
-#pragma unroll
-                        for (uint32_t u = 0; u < kUnroll; ++u)
-                            if (u < nu)
-                                ok = ok && mbar_wait(b_full0 + 8 * js[u], pbs[u], s_abort) && mbar_wait(a_full0 + 8 * ks[u], pas[u], s_abort);
+                        ok = mbar_wait(b_full0 + 8 * j, pb, s_abort) && mbar_wait(a_full0 + 8 * k, pa, s_abort);
+                        if (!ok) break;
                     }
-                    if (!ok) break;
+                    uint32_t k2 = k + 1, pa2 = pa, j2 = j + 1, pb2 = pb;
+                    if (k2 == SA) { k2 = 0; pa2 ^= 1; }
+                    if (j2 == SB) { j2 = 0; pb2 ^= 1; }
+                    bool next_ready = false;
+                    if (i + 1 < it.nslab) next_ready = mbar_test2(b_full0 + 8 * j2, pb2, a_full0 + 8 * k2, pa2);
                     tc_fence_after_sync();
                     if (elect_one()) {
+                        // descriptors differ from slot 0's only in the 16-byte-unit address field
+                        const uint32_t b_lo = b_lo0 + j * (kBBytes >> 4);
+                        if constexpr (A_TMEM) {
+                            const uint32_t ta = tmem_base + kATmemBase + k * 32;
 #pragma unroll
-                        for (uint32_t u = 0; u < kUnroll; ++u) {
-                            if (u >= nu) continue;
-                            // descriptors differ from slot 0's only in the 16-byte-unit address field
-                            const uint32_t b_lo = b_lo0 + js[u] * (kBBytes >> 4);
-                            if constexpr (A_TMEM) {
-                                const uint32_t ta = tmem_base + kATmemBase + ks[u] * 32;
+                            for (uint32_t kk = 0; kk < kSlabK / 32; ++kk)  // 32 bytes of K = 8 TMEM columns of A
+                                umma_i8_ts(d_tmem, ta + 8 * kk, ((uint64_t)desc_hi << 32) | (b_lo + 2 * kk), kIdesc,
+                                           (i | kk) != 0 ? 1u : 0u);
+                        } else {
+                            const uint32_t a_lo = a_lo0 + k * (kABytes >> 4);
 #pragma unroll
-                                for (uint32_t kk = 0; kk < kSlabK / 32; ++kk)  // 32 bytes of K = 8 TMEM columns of A
-                                    umma_i8_ts(d_tmem, ta + 8 * kk, ((uint64_t)desc_hi << 32) | (b_lo + 2 * kk), kIdesc,
-                                               (i | u | kk) != 0 ? 1u : 0u);
-                            } else {
-                                const uint32_t a_lo = a_lo0 + ks[u] * (kABytes >> 4);
-#pragma unroll
-                                for (uint32_t kk = 0; kk < kSlabK / 32; ++kk)  // 32 bytes of K per instruction
-                                    umma_i8(d_tmem, ((uint64_t)desc_hi << 32) | (a_lo + 2 * kk),
-                                            ((uint64_t)desc_hi << 32) | (b_lo + 2 * kk), kIdesc, (i | u | kk) != 0 ? 1u : 0u);
-                            }
-                            umma_commit(a_empty0 + 8 * ks[u]);  // each slot is free once these MMAs have read it
-                            umma_commit(b_empty0 + 8 * js[u]);
+                            for (uint32_t kk = 0; kk < kSlabK / 32; ++kk)  // 32 bytes of K per instruction
+                                umma_i8(d_tmem, ((uint64_t)desc_hi << 32) | (a_lo + 2 * kk),
+                                        ((uint64_t)desc_hi << 32) | (b_lo + 2 * kk), kIdesc, (i | kk) != 0 ? 1u : 0u);
                         }
+                        umma_commit(a_empty0 + 8 * k);  // each slot is free once these MMAs have read it
+                        umma_commit(b_empty0 + 8 * j);
                     }
                     __syncwarp();
+                    k = k2; pa = pa2; j = j2; pb = pb2;
+                    ready = next_ready;
                 }
                 if (ok && elect_one()) umma_commit(acc_full0 + 8 * ab);
                 __syncwarp();
@@ -725,7 +708,7 @@ cudaError_t launch_umma(const LutArgs& a, const CUtensorMap& lut_t_map, const Um
     p.a_slots_log2 = 0;
     while ((1u << p.a_slots_log2) < p.a_slots) ++p.a_slots_log2;
     // slabs a builder group takes per turn
-    uint32_t sps = plan.sps == 1 ? 1u : (plan.sps >= 2 ? 2u : (p.a_slots >= 8 ? 2u : 1u));
+    uint32_t sps = plan.sps >= 2 ? 2u : 1u;  // one measured at least as fast as two on every benchmark shape
     if (sps > p.a_slots / 2) sps = 1;
     p.tiles_m = (a.M + kMTile - 1) / kMTile;
     p.tiles_n = (a.N + plan.n_tile - 1) / plan.n_tile;

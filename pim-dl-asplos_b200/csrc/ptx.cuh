@@ -49,24 +49,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Non-blocking probe of four barriers at once: true if every one has completed the phase with
-// its parity.  A single query takes a round trip of the order of a hundred cycles before its
-// answer can be used; issued back to back the four overlap.
-__device__ __forceinline__ bool mbar_test4(uint32_t b0, uint32_t p0, uint32_t b1, uint32_t p1, uint32_t b2, uint32_t p2,
-                                           uint32_t b3, uint32_t p3) {
+// Non-blocking probe of two barriers at once: true if both have completed the phase with their
+// parity.  A query takes a round trip of the order of a hundred cycles before its answer can be
+// used; issued back to back the two overlap, and a loop that needs the answer every turn asks one
+// turn ahead.
+__device__ __forceinline__ bool mbar_test2(uint32_t b0, uint32_t p0, uint32_t b1, uint32_t p1) {
     uint32_t ok;
     asm volatile(
-        "{\n\t.reg .pred q0, q1, q2, q3;\n\t"
+        "{\n\t.reg .pred q0, q1;\n\t"
         "mbarrier.test_wait.parity.shared::cta.b64 q0, [%1], %2;\n\t"
         "mbarrier.test_wait.parity.shared::cta.b64 q1, [%3], %4;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 q2, [%5], %6;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 q3, [%7], %8;\n\t"
         "and.pred q0, q0, q1;\n\t"
-        "and.pred q2, q2, q3;\n\t"
-        "and.pred q0, q0, q2;\n\t"
         "selp.u32 %0, 1, 0, q0;\n\t}"
         : "=r"(ok)
-        : "r"(b0), "r"(p0), "r"(b1), "r"(p1), "r"(b2), "r"(p2), "r"(b3), "r"(p3)
+        : "r"(b0), "r"(p0), "r"(b1), "r"(p1)
         : "memory");
     return ok != 0;
 }
