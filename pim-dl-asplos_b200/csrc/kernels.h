@@ -61,7 +61,8 @@ bool umma_supported(uint32_t CB, uint32_t CT, uint32_t N);
 bool umma_tile_ok(uint32_t n_tile, bool a_tmem);
 cudaError_t umma_make_tmap(CUtensorMap* out, const int8_t* lut_t, uint32_t CB, uint32_t CT, uint32_t N,
                            uint32_t n_tile, const char** why);
-// `acc_scratch` (int32 [split][M][N]) and `tile_counters` (zeroed once) are needed when split > 1.
+// `acc_scratch` (int32 [split][M][N]) and `tile_counters` (two words per output tile, zeroed once)
+// are needed when split > 1.
 cudaError_t launch_umma(const LutArgs& a, const CUtensorMap& lut_t_map, const UmmaPlan& p, int32_t* acc_scratch,
                         uint32_t* tile_counters, uint32_t* dev_err, cudaStream_t s, const char** why);
 void umma_default_plan(uint32_t M, uint32_t CB, uint32_t CT, uint32_t N, int sm_count, uint32_t operand,

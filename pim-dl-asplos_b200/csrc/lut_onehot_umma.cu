@@ -480,19 +480,29 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
                 }
             }
             if (p.split > 1) {
-                // The CTA that arrives last at this output tile sums the slices and dequantises.  Every epilogue thread runs the barriers, also after a
-                // failed wait, so nobody is left behind at one.
+                // The CTAs that hold the slices of an output tile sum them together: each waits (bounded)
+                // until all slices are in the scratch buffer, then sums and dequantises its share of
+                // the tile's rows - row pass p of every 32-row quadrant goes to slice p % split.  (One
+                // CTA summing the whole tile took longer than the main loop of a short slice.)  The
+                // grid never exceeds one CTA per SM and a CTA takes its items in increasing order, so
+                // the slices of a tile are in progress or done when one of them waits here.
+                // Every epilogue thread runs the barriers, also after a failed wait, so nobody is left
+                // behind at one.
                 __threadfence();
                 named_bar_sync(1, kEpiThreads);
+                uint32_t* ctr = p.tile_counters + 2 * it.tile;  // [0] slices arrived, [1] slices done
                 if (et == 0) {
-                    uint32_t last = 0;
+                    uint32_t go = 0;
                     if (ok && !*s_abort) {
-                        uint32_t* ctr = p.tile_counters + it.tile;
-                        const uint32_t old = atomicAdd(ctr, 1u);
-                        last = (old == p.split - 1) ? 1u : 0u;
-                        if (last) *ctr = 0u;
+                        atomicAdd(ctr, 1u);
+                        for (uint32_t spin = 0; spin < kWaitLimit; ++spin) {
+                            if (*reinterpret_cast<volatile uint32_t*>(ctr) >= p.split) { go = 1; break; }
+                            if ((spin & 63u) == 63u && *s_abort) break;
+                            __nanosleep(64);
+                        }
+                        if (!go) *s_abort = 1u;
                     }
-                    s_misc[2] = last;
+                    s_misc[2] = go;
                 }
                 named_bar_sync(1, kEpiThreads);
                 if (s_misc[2]) {
@@ -500,8 +510,7 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
                     // All loads of a row first, then the stores: the loop is a chain of L2 round
                     // trips otherwise.
                     constexpr uint32_t kChunks = N_TILE / 32;
-#pragma unroll 2
-                    for (uint32_t pass = 0; pass < 8; ++pass) {
+                    for (uint32_t pass = it.z; pass < 8; pass += p.split) {
                         const uint32_t mm = it.m0 + quad * 32 + pass * 4 + rsub;
                         if (mm >= a.M) continue;
                         int4 val[kChunks];
@@ -538,6 +547,10 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
                     }
                 }
                 named_bar_sync(1, kEpiThreads);  // s_misc[2] is rewritten by the next item
+                // the slice that finishes last re-arms the tile's counters for the next launch
+                if (et == 0 && s_misc[2]) {
+                    if (atomicAdd(ctr + 1, 1u) == p.split - 1) { ctr[0] = 0u; ctr[1] = 0u; }
+                }
             }
         }
         tc_fence_before_sync();

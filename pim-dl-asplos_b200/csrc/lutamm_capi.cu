@@ -226,7 +226,7 @@ int run_lut(lutamm_ctx* c, Layer& L, const uint8_t* d_idx, float* d_out, int32_t
             const uint32_t tiles = ((M + 127) / 128) * ((L.N + up.n_tile - 1) / up.n_tile);
             int r = ensure(c, c->d_acc_scratch, (size_t)up.split * M * L.N * sizeof(int32_t), false);
             if (r) return r;
-            r = ensure(c, c->d_counters, (size_t)tiles * sizeof(uint32_t), true);
+            r = ensure(c, c->d_counters, (size_t)tiles * 2 * sizeof(uint32_t), true);  // arrived / done per tile
             if (r) return r;
         }
         cudaError_t e = launch_umma(a, L.umma_maps[slot], up, static_cast<int32_t*>(c->d_acc_scratch.p),
@@ -279,6 +279,8 @@ int check_dev_err(lutamm_ctx* c) {
     if (*c->h_err) {
         const uint32_t code = *c->h_err;
         cudaMemsetAsync(c->d_err, 0, sizeof(uint32_t), c->stream);
+        // a kernel that gave up may have left split-K tile counters half counted
+        if (c->d_counters.p) cudaMemsetAsync(c->d_counters.p, 0, c->d_counters.cap, c->stream);
         return fail(c, LUTAMM_EDEVICE, "a kernel gave up on a bounded wait (code " + std::to_string(code) + "); output is not valid");
     }
     return LUTAMM_OK;
