@@ -150,6 +150,18 @@ int lutamm_load_weights(lutamm_ctx* ctx, int layer_id,
                         const lutamm_index_params* index_params,
                         const lutamm_lut_params* lut_params);
 
+/* The same with the LUT in a stated layout.  LUTAMM_LUT_DPU_TILED is the table exactly as the
+ * reference's callers hold it after reorder_pim_lut() (inference-engine/test/test_amm.cpp:71-121;
+ * the layer tests re-tile the same way): re-tiled along the output features with tile width
+ * feature_stile_size (lut_load_type STATIC) or feature_load_tile_size (FINE / COARSE_GRAIN), which
+ * must divide output_feature_len.  It is un-tiled on the device at load time. */
+#define LUTAMM_LUT_CANONICAL 0u
+#define LUTAMM_LUT_DPU_TILED 1u
+int lutamm_load_weights_layout(lutamm_ctx* ctx, int layer_id,
+                               const float* centroid, const int8_t* lut, const float* bias,
+                               const lutamm_index_params* index_params,
+                               const lutamm_lut_params* lut_params, uint32_t lut_layout);
+
 int lutamm_unload_weights(lutamm_ctx* ctx, int layer_id);
 
 /* Build one linear layer's int8 lookup table from its centroids and its dense weight on the GPU.

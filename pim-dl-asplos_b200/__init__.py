@@ -21,6 +21,7 @@ OK, EINVAL, ECUDA, ENOLAYER, EUNSUPPORTED, EDEVICE, ENOMEM = 0, -1, -2, -3, -4, 
 FLAG_ASYNC, FLAG_OUTPUT_TILED = 1, 2
 VARIANT_AUTO, VARIANT_GATHER, VARIANT_UMMA = 0, 1, 2
 INDEX_U8_ROWMAJOR, INDEX_U16_TILED = 0, 1
+LUT_CANONICAL, LUT_DPU_TILED = 0, 1
 
 # every symbol include/lutamm.h declares
 ABI_SYMBOLS = [
@@ -29,6 +30,7 @@ ABI_SYMBOLS = [
     "lutamm_index_calculation", "lutamm_pim_lut", "lutamm_set_plan", "lutamm_get_plan", "lutamm_tune",
     "lutamm_enable_timing", "lutamm_get_timings", "lutamm_launch_count",
     "lutamm_amm_static_scratch", "lutamm_static_scratch_last_error", "lutamm_build_lut",
+    "lutamm_load_weights_layout",
 ]
 
 
@@ -98,6 +100,8 @@ def load_library() -> ctypes.CDLL:
     L.lutamm_last_error.argtypes = [vp]
     L.lutamm_last_error.restype = ctypes.c_char_p
     L.lutamm_load_weights.argtypes = [vp, i32, vp, vp, vp, ctypes.POINTER(IndexCalcParams), ctypes.POINTER(LUTParams)]
+    L.lutamm_load_weights_layout.argtypes = [vp, i32, vp, vp, vp, ctypes.POINTER(IndexCalcParams),
+                                             ctypes.POINTER(LUTParams), u32]
     L.lutamm_unload_weights.argtypes = [vp, i32]
     L.lutamm_build_lut.argtypes = [vp, vp, vp, u32, u32, u32, u32, vp, ctypes.POINTER(ctypes.c_float),
                                    ctypes.POINTER(ctypes.c_float)]
@@ -138,7 +142,8 @@ def _ptr(a) -> int:
 
 def make_params(M: int, K: int, N: int, CB: int, CT: int, scale: float, lut_bias: float = 0.0, *,
                 n_stile: int | None = None, f_stile: int | None = None, n_mtile: int | None = None,
-                f_mtile: int | None = None, cb_mtile: int | None = None, num_threads: int = 1):
+                f_mtile: int | None = None, cb_mtile: int | None = None, num_threads: int = 1,
+                lut_load_type: int = 0, f_load: int | None = None, cb_load: int | None = None):
     """Parameter blocks as parse_amm_configs() would fill them (src/host/parser.cpp:22-46).
     Tile sizes default to "one tile": the canonical row-major layouts."""
     n_stile = n_stile or max(M, 1)
@@ -156,8 +161,8 @@ def make_params(M: int, K: int, N: int, CB: int, CT: int, scale: float, lut_bias
     lp.dpu_num = lp.input_parallelism * lp.lut_parallelism
     lp.feature_stile_size, lp.n_stile_size = f_stile, n_stile
     lp.n_mtile_size, lp.feature_mtile_size, lp.cb_mtile_size = n_mtile, f_mtile, cb_mtile
-    lp.lut_load_type = 0
-    lp.feature_load_tile_size, lp.cb_load_tile_size = f_mtile, cb_mtile
+    lp.lut_load_type = lut_load_type
+    lp.feature_load_tile_size, lp.cb_load_tile_size = f_load or f_mtile, cb_load or cb_mtile
     return ip, lp
 
 
@@ -219,15 +224,17 @@ class LutAmmContext:
 
     # -- weights
     def load_weights(self, layer_id: int, centroid, lut, bias, scale: float, lut_bias: float = 0.0,
-                     ip: IndexCalcParams | None = None, lp: LUTParams | None = None):
-        """centroid [CB][CT][v] fp32, lut [CB][CT][N] int8, bias [N] fp32 (numpy or torch)."""
+                     ip: IndexCalcParams | None = None, lp: LUTParams | None = None, lut_layout: int = LUT_CANONICAL):
+        """centroid [CB][CT][v] fp32, lut [CB][CT][N] int8, bias [N] fp32 (numpy or torch).  With
+        lut_layout=LUT_DPU_TILED `lut` is the flat table after the reference's reorder_pim_lut()
+        (test/test_amm.cpp:71-121) and `lp` carries the tile sizes."""
         CB, CT, v = tuple(centroid.shape)
-        N = int(lut.shape[2])
+        N = int(lut.shape[2]) if lut_layout == LUT_CANONICAL else int(lp.output_feature_len)
         K = CB * v
         if ip is None or lp is None:
             ip, lp = make_params(0, K, N, CB, CT, scale, lut_bias)
-        self._check(self._L.lutamm_load_weights(self._h, layer_id, _ptr(centroid), _ptr(lut), _ptr(bias),
-                                                ctypes.byref(ip), ctypes.byref(lp)))
+        self._check(self._L.lutamm_load_weights_layout(self._h, layer_id, _ptr(centroid), _ptr(lut), _ptr(bias),
+                                                       ctypes.byref(ip), ctypes.byref(lp), lut_layout))
         self.layers[layer_id] = _LayerInfo(K, N, CB, CT, ip, lp)
 
     def build_lut(self, centroid, weight, lut_out=None):

@@ -23,8 +23,28 @@ constexpr int kFirstAutoId = 1 << 20;
 
 }  // namespace
 
+namespace {
+int amm_host_impl(lutamm_ctx* ctx, float* input_tensor, float* centroid_tensor, lut_data_type* lut_table,
+                  float* bias_tensor, float* output_tensor, IndexCalcParams index_params, LUTParams lut_params,
+                  uint32_t lut_layout, uint32_t flags);
+}
+
 int amm_host(lutamm_ctx* ctx, float* input_tensor, float* centroid_tensor, lut_data_type* lut_table,
              float* bias_tensor, float* output_tensor, IndexCalcParams index_params, LUTParams lut_params) {
+    return amm_host_impl(ctx, input_tensor, centroid_tensor, lut_table, bias_tensor, output_tensor, index_params,
+                         lut_params, LUTAMM_LUT_CANONICAL, 0);
+}
+
+int amm_host_dpu_layout(lutamm_ctx* ctx, float* input_tensor, float* centroid_tensor, lut_data_type* dpu_lut_table,
+                        float* bias_tensor, float* output_tensor, IndexCalcParams index_params, LUTParams lut_params) {
+    return amm_host_impl(ctx, input_tensor, centroid_tensor, dpu_lut_table, bias_tensor, output_tensor, index_params,
+                         lut_params, LUTAMM_LUT_DPU_TILED, LUTAMM_FLAG_OUTPUT_TILED);
+}
+
+namespace {
+int amm_host_impl(lutamm_ctx* ctx, float* input_tensor, float* centroid_tensor, lut_data_type* lut_table,
+                  float* bias_tensor, float* output_tensor, IndexCalcParams index_params, LUTParams lut_params,
+                  uint32_t lut_layout, uint32_t flags) {
     int id;
     {
         std::lock_guard<std::mutex> lk(g_mu);
@@ -34,17 +54,18 @@ int amm_host(lutamm_ctx* ctx, float* input_tensor, float* centroid_tensor, lut_d
             int& next = g_next_id[ctx];
             if (next < kFirstAutoId) next = kFirstAutoId;
             id = next++;
-            const int rc = lutamm_load_weights(ctx, id, centroid_tensor, lut_table, bias_tensor,
-                                               reinterpret_cast<const lutamm_index_params*>(&index_params),
-                                               reinterpret_cast<const lutamm_lut_params*>(&lut_params));
+            const int rc = lutamm_load_weights_layout(ctx, id, centroid_tensor, lut_table, bias_tensor,
+                                                      reinterpret_cast<const lutamm_index_params*>(&index_params),
+                                                      reinterpret_cast<const lutamm_lut_params*>(&lut_params), lut_layout);
             if (rc != LUTAMM_OK) return rc;
             g_layers.emplace(k, id);
         } else {
             id = it->second;
         }
     }
-    return lutamm_amm(ctx, id, input_tensor, output_tensor, index_params.n, 0);
+    return lutamm_amm(ctx, id, input_tensor, output_tensor, index_params.n, flags);
 }
+}  // namespace
 
 int index_calculation(lutamm_ctx* ctx, int layer_id, float* input_tensor, uint8_t* lut_input_index, uint32_t n) {
     return lutamm_index_calculation(ctx, layer_id, input_tensor, lut_input_index, n, LUTAMM_INDEX_U8_ROWMAJOR);

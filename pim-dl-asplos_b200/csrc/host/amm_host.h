@@ -15,6 +15,14 @@
 int amm_host(lutamm_ctx* ctx, float* input_tensor, float* centroid_tensor, lut_data_type* lut_table,
              float* bias_tensor, float* output_tensor, IndexCalcParams index_params, LUTParams lut_params);
 
+// The same operator with the reference's DATA contract as well: `lut_table` is the table after
+// reorder_pim_lut() (test/test_amm.cpp:71-121, re-tiled per lut_params.lut_load_type and tile sizes)
+// and `output_tensor` receives the DPU-tiled layout the reference returns
+// (pim_lut_host.cpp:173-203, read back through test/test_amm.cpp:193-202).  A caller written
+// against the reference passes its buffers unchanged.
+int amm_host_dpu_layout(lutamm_ctx* ctx, float* input_tensor, float* centroid_tensor, lut_data_type* dpu_lut_table,
+                        float* bias_tensor, float* output_tensor, IndexCalcParams index_params, LUTParams lut_params);
+
 // The two halves, as in index_calc_host.h:5 and pim_lut_host.h:14-15.  `layer_id` names
 // weights loaded with lutamm_load_weights(); the index buffer is uint8 [n][num_codebook].
 int index_calculation(lutamm_ctx* ctx, int layer_id, float* input_tensor, uint8_t* lut_input_index, uint32_t n);

@@ -85,6 +85,10 @@ struct LutBuildArgs {
 // Three launches on `s`: abs-max pass, quantising pass, scalar finish.
 cudaError_t launch_lut_build(const LutBuildArgs& a, cudaStream_t s, const char** why);
 
+// LUT in the reference's DPU layout (re-tiled along the output features, tile width T) -> canonical.
+cudaError_t launch_lut_untile(const int8_t* dpu, int8_t* canonical, uint32_t rows, uint32_t N, uint32_t T,
+                              cudaStream_t s, const char** why);
+
 // Driver entry point for tensor-map encoding, resolved through the runtime so the library
 // carries no link-time dependency on the driver and loads on machines without one.
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,

@@ -111,6 +111,36 @@ __global__ void lut_build_finish_kernel(const uint32_t* absmax_bits, float* scal
 
 }  // namespace
 
+// The reference keeps the LUT it sends to the DPUs re-tiled along the output features
+// (reorder_pim_lut, inference-engine/test/test_amm.cpp:71-121):
+//   dpu[(f / T) * rows * T + row * T + f % T] = canonical[row * N + f],   row = cb * CT + ct,
+// T = feature_stile_size (STATIC load type) or feature_load_tile_size (FINE / COARSE).  This
+// turns such a table back into the canonical [CB][CT][N] layout the kernels read.
+namespace {
+__global__ void lut_untile_kernel(const int8_t* __restrict__ dpu, int8_t* __restrict__ canonical, uint32_t rows,
+                                  uint32_t N, uint32_t T) {
+    const uint32_t row = blockIdx.y;
+    for (uint32_t f = blockIdx.x * blockDim.x + threadIdx.x; f < N; f += gridDim.x * blockDim.x)
+        canonical[(size_t)row * N + f] = dpu[(size_t)(f / T) * rows * T + (size_t)row * T + f % T];
+}
+}  // namespace
+
+cudaError_t launch_lut_untile(const int8_t* dpu, int8_t* canonical, uint32_t rows, uint32_t N, uint32_t T,
+                              cudaStream_t s, const char** why) {
+    *why = nullptr;
+    if (T == 0 || N % T != 0) { *why = "output_feature_len must be a multiple of the LUT tile width"; return cudaErrorInvalidValue; }
+    if (rows == 0 || rows > 65535u * 32u) { *why = "LUT has too many rows"; return cudaErrorInvalidValue; }
+    // rows can exceed the 65535 limit of grid.y: fold the excess into a loop over row blocks
+    const uint32_t per = 65535u;
+    for (uint32_t r0 = 0; r0 < rows; r0 += per) {
+        const uint32_t nr = rows - r0 < per ? rows - r0 : per;
+        const dim3 grid((N + 255) / 256 > 64 ? 64 : (N + 255) / 256, nr);
+        // the tile term of the source index uses the full row count, the row term the absolute row
+        lut_untile_kernel<<<grid, 256, 0, s>>>(dpu + (size_t)r0 * T, canonical + (size_t)r0 * N, rows, N, T);
+    }
+    return cudaGetLastError();
+}
+
 cudaError_t launch_lut_build(const LutBuildArgs& a, cudaStream_t s, const char** why) {
     *why = nullptr;
     if (a.v == 0 || a.v > kMaxV) { *why = "sub-vector length must be 1..1024"; return cudaErrorInvalidValue; }

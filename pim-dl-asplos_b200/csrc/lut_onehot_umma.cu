@@ -45,8 +45,9 @@ constexpr uint32_t kABytes = kMTile * kSlabK;  // 16 KiB
 constexpr uint32_t kMaxAgenGroups = 4;  // each group: 4 warps = 128 rows (more groups measured slower)
 constexpr uint32_t kEpiWarps = 4;
 constexpr uint32_t kEpiThreads = kEpiWarps * 32;
-constexpr uint32_t kFirstAgenWarp = 2;
-constexpr uint32_t kMaxThreads = (kFirstAgenWarp + 4 * kMaxAgenGroups + kEpiWarps) * 32;  // 704
+constexpr uint32_t kMmaWarps = 2;      // MMA-issuing warps: slab x of the CTA's sequence is issued by warp x % 2
+constexpr uint32_t kFirstAgenWarp = 1 + kMmaWarps;
+constexpr uint32_t kMaxThreads = (kFirstAgenWarp + 4 * kMaxAgenGroups + kEpiWarps) * 32;  // 736
 constexpr uint32_t kMaxASlots = 8;    // one-hot slabs in flight (tensor memory: 32 columns each)
 constexpr uint32_t kMaxBSlots = 16;   // LUT slabs in flight (shared memory)
 constexpr uint32_t kNumBarriers = 2 * kMaxASlots + 2 * kMaxBSlots + 4;
@@ -153,7 +154,7 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
             mbar_init(b_empty0 + 8 * j, 1);  // tcgen05.commit
         }
         for (uint32_t b = 0; b < 2; ++b) {
-            mbar_init(acc_full0 + 8 * b, 1);           // tcgen05.commit
+            mbar_init(acc_full0 + 8 * b, kMmaWarps);   // one tcgen05.commit per issuing warp
             mbar_init(acc_empty0 + 8 * b, kEpiWarps);
         }
         fence_barrier_init();
@@ -172,6 +173,17 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(s_misc);
+    // Every MMA accumulates (two warps issue them, in no fixed order), so the accumulators start at
+    // zero: the epilogue warps clear both here and clear each again after reading it.
+    if (warp >= kFirstEpiWarp) {
+        const uint32_t zero[32] = {};
+        for (uint32_t c = 0; c < 2 * N_TILE / 32; ++c)
+            tmem_st_32x32b_x32(tmem_base + (((warp & 3u) * 32u) << 16) + c * 32u, zero);
+        tmem_st_wait();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
 
     if (warp == 0) {
         // ---------------- TMA producer (the LUT never depends on the preceding kernel)
@@ -191,39 +203,43 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
             }
         }
         __syncwarp();
-    } else if (warp == 1) {
-        // ---------------- MMA issuer: the whole warp walks the loop converged (waits and
-        // descriptor arithmetic stay warp-uniform; a lone lane running the loop measured 20 %
-        // slower), one elected lane issues.  Per slab: four tcgen05.mma (32 bytes of K each), then
-        // one commit per ring hands the two slots back.  (Turns of two or four slabs measured
-        // slower: the one-hot ring is too shallow to have that many slabs ready at once.)
+    } else if (warp < kFirstAgenWarp) {
+        // ---------------- MMA issuers: two warps, slab x of the CTA's sequence goes to warp x % 2.
+        // A slab's turn (barrier probes, fence, election, four tcgen05.mma of 32 bytes of K each, one
+        // commit per ring) costs the issuing warp about 600 cycles, more than the four MMAs take to
+        // execute; two warps taking turns keep the tensor pipe fed.  All MMAs accumulate into an
+        // accumulator the epilogue left at zero, integer addition commutes, so the order in which
+        // the two warps' instructions reach the pipe does not matter.  Each warp walks its loop
+        // converged (waits and descriptor arithmetic stay warp-uniform; a lone lane running the
+        // loop measured 20 % slower), one elected lane issues.
         {
-            uint32_t k = 0, pa = 0, j = 0, pb = 0, t = 0;
+            const uint32_t me = warp - 1;
+            const uint32_t sa_mask = SA - 1, sa_log2 = p.a_slots_log2;
+            uint32_t j = me % SB, pb = 0, t = 0, x0 = 0;  // LUT slot / phase of this warp's next slab; slabs before the item
             bool ok = true;
             const uint32_t b_lo0 = (uint32_t)umma_desc_k_sw128(smem_u32(s_b));
             const uint32_t a_lo0 = (uint32_t)umma_desc_k_sw128(smem_u32(s_a));
             const uint32_t desc_hi = (uint32_t)(umma_desc_k_sw128(0) >> 32);
+            // Whether a slab's two slots are full is asked one turn ahead: a barrier query is a round
+            // trip of the order of a hundred cycles.
+            bool ready = mbar_test2(b_full0 + 8 * j, pb, a_full0 + 8 * (me & sa_mask), (me >> sa_log2) & 1u);
             for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++t) {
                 const Item it = decode_item(p, item, N_TILE);
                 const uint32_t ab = t & 1, aph = (t >> 1) & 1;
-                ok = mbar_wait(acc_empty0 + 8 * ab, aph ^ 1, s_abort);  // epilogue drained this buffer
+                ok = mbar_wait(acc_empty0 + 8 * ab, aph ^ 1, s_abort);  // epilogue drained and cleared this buffer
                 if (!ok) break;
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + ab * N_TILE;
-                // Whether slab i's two slots are full is asked while slab i-1 is being issued: a barrier
-                // query is a round trip of the order of a hundred cycles, and two of them in front of
-                // every slab's instructions cost more than the slab's four MMAs take to execute.
-                bool ready = mbar_test2(b_full0 + 8 * j, pb, a_full0 + 8 * k, pa);
-                for (uint32_t i = 0; i < it.nslab; ++i) {
+                for (uint32_t i = (x0 + me) & 1u; i < it.nslab; i += 2) {
+                    const uint32_t x = x0 + i, k = x & sa_mask, pa = (x >> sa_log2) & 1u;
                     if (!ready) {
                         ok = mbar_wait(b_full0 + 8 * j, pb, s_abort) && mbar_wait(a_full0 + 8 * k, pa, s_abort);
                         if (!ok) break;
                     }
-                    uint32_t k2 = k + 1, pa2 = pa, j2 = j + 1, pb2 = pb;
-                    if (k2 == SA) { k2 = 0; pa2 ^= 1; }
-                    if (j2 == SB) { j2 = 0; pb2 ^= 1; }
-                    bool next_ready = false;
-                    if (i + 1 < it.nslab) next_ready = mbar_test2(b_full0 + 8 * j2, pb2, a_full0 + 8 * k2, pa2);
+                    uint32_t j2 = j + 2, pb2 = pb;
+                    if (j2 >= SB) { j2 -= SB; pb2 ^= 1; }
+                    const uint32_t x2 = x + 2;
+                    const bool next_ready = mbar_test2(b_full0 + 8 * j2, pb2, a_full0 + 8 * (x2 & sa_mask), (x2 >> sa_log2) & 1u);
                     tc_fence_after_sync();
                     if (elect_one()) {
                         // descriptors differ from slot 0's only in the 16-byte-unit address field
@@ -232,23 +248,23 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
                             const uint32_t ta = tmem_base + kATmemBase + k * 32;
 #pragma unroll
                             for (uint32_t kk = 0; kk < kSlabK / 32; ++kk)  // 32 bytes of K = 8 TMEM columns of A
-                                umma_i8_ts(d_tmem, ta + 8 * kk, ((uint64_t)desc_hi << 32) | (b_lo + 2 * kk), kIdesc,
-                                           (i | kk) != 0 ? 1u : 0u);
+                                umma_i8_ts(d_tmem, ta + 8 * kk, ((uint64_t)desc_hi << 32) | (b_lo + 2 * kk), kIdesc, 1u);
                         } else {
                             const uint32_t a_lo = a_lo0 + k * (kABytes >> 4);
 #pragma unroll
                             for (uint32_t kk = 0; kk < kSlabK / 32; ++kk)  // 32 bytes of K per instruction
                                 umma_i8(d_tmem, ((uint64_t)desc_hi << 32) | (a_lo + 2 * kk),
-                                        ((uint64_t)desc_hi << 32) | (b_lo + 2 * kk), kIdesc, (i | kk) != 0 ? 1u : 0u);
+                                        ((uint64_t)desc_hi << 32) | (b_lo + 2 * kk), kIdesc, 1u);
                         }
                         umma_commit(a_empty0 + 8 * k);  // each slot is free once these MMAs have read it
                         umma_commit(b_empty0 + 8 * j);
                     }
                     __syncwarp();
-                    k = k2; pa = pa2; j = j2; pb = pb2;
+                    j = j2; pb = pb2;
                     ready = next_ready;
                 }
-                if (ok && elect_one()) umma_commit(acc_full0 + 8 * ab);
+                x0 += it.nslab;
+                if (ok && elect_one()) umma_commit(acc_full0 + 8 * ab);  // this warp's share of the item is issued
                 __syncwarp();
             }
         }
@@ -413,7 +429,12 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
                     uint32_t v[32];
                     tmem_ld_32x32b_x32(tmem_base + ((quad * 32u) << 16) + ab * N_TILE + c * 32u, v);
                     tmem_ld_wait();
-                    if (c == N_TILE / 32 - 1) {  // accumulator fully read: hand the buffer back
+                    {   // leave the columns at zero for the next item's accumulating MMAs
+                        const uint32_t zero[32] = {};
+                        tmem_st_32x32b_x32(tmem_base + ((quad * 32u) << 16) + ab * N_TILE + c * 32u, zero);
+                    }
+                    if (c == N_TILE / 32 - 1) {  // accumulator fully read and cleared: hand the buffer back
+                        tmem_st_wait();
                         tc_fence_before_sync();
                         __syncwarp();
                         if (lane == 0) mbar_arrive(acc_empty0 + 8 * ab);

@@ -485,6 +485,11 @@ const char* lutamm_last_error(const lutamm_ctx* c) { return c ? c->err.c_str() :
 
 int lutamm_load_weights(lutamm_ctx* c, int layer_id, const float* centroid, const int8_t* lut, const float* bias,
                         const lutamm_index_params* ip, const lutamm_lut_params* lp) {
+    return lutamm_load_weights_layout(c, layer_id, centroid, lut, bias, ip, lp, LUTAMM_LUT_CANONICAL);
+}
+
+int lutamm_load_weights_layout(lutamm_ctx* c, int layer_id, const float* centroid, const int8_t* lut, const float* bias,
+                               const lutamm_index_params* ip, const lutamm_lut_params* lp, uint32_t lut_layout) {
     if (!c) return fail(nullptr, LUTAMM_EINVAL, "null context");
     if (!centroid || !lut || !bias || !ip || !lp) return fail(c, LUTAMM_EINVAL, "null argument");
     const uint32_t K = ip->input_feature_len, CB = ip->num_codebook, CT = ip->num_centroid, N = lp->output_feature_len;
@@ -495,6 +500,7 @@ int lutamm_load_weights(lutamm_ctx* c, int layer_id, const float* centroid, cons
         return fail(c, LUTAMM_EINVAL, "sub_vec_len != input_feature_len / num_codebook (parser.cpp:26)");
     if (lp->num_codebook != CB || lp->num_centroid != CT)
         return fail(c, LUTAMM_EINVAL, "index and LUT parameter blocks disagree on num_codebook / num_centroid");
+    if (lut_layout != LUTAMM_LUT_CANONICAL && lut_layout != LUTAMM_LUT_DPU_TILED) return fail(c, LUTAMM_EINVAL, "unknown LUT layout");
     if (CT > 256) return fail(c, LUTAMM_EINVAL, "num_centroid > 256 does not fit the uint8 index");
     if (N % 16) return fail(c, LUTAMM_EINVAL, "output_feature_len must be a multiple of 16");
     if ((uint64_t)CB * CT * N >= (1ull << 40)) return fail(c, LUTAMM_EINVAL, "LUT too large");
@@ -514,7 +520,23 @@ int lutamm_load_weights(lutamm_ctx* c, int layer_id, const float* centroid, cons
         return fail(c, LUTAMM_ENOMEM, std::string("cudaMalloc for weights: ") + cudaGetErrorString(e));
     }
     CU_TRY(c, cudaMemcpyAsync(L.d_centroid, centroid, cb, cudaMemcpyDefault, c->stream));
-    CU_TRY(c, cudaMemcpyAsync(L.d_lut, lut, lb, cudaMemcpyDefault, c->stream));
+    if (lut_layout == LUTAMM_LUT_DPU_TILED) {
+        // the table as the reference sends it to the DPUs: stage it, then un-tile on the device
+        const uint32_t T = lp->lut_load_type == 0 ? lp->feature_stile_size : lp->feature_load_tile_size;
+        int r = ensure(c, c->d_build, lb);
+        if (r) { free_layer(L); c->layers.erase(layer_id); return r; }
+        CU_TRY(c, cudaMemcpyAsync(c->d_build.p, lut, lb, cudaMemcpyDefault, c->stream));
+        const char* why = nullptr;
+        cudaError_t ue = launch_lut_untile(static_cast<const int8_t*>(c->d_build.p), L.d_lut, CB * CT, N, T, c->stream, &why);
+        if (ue != cudaSuccess) {
+            free_layer(L);
+            c->layers.erase(layer_id);
+            return fail(c, why ? LUTAMM_EINVAL : LUTAMM_ECUDA, why ? std::string(why) : std::string("LUT un-tiling: ") + cudaGetErrorString(ue));
+        }
+        c->launches += 1;
+    } else {
+        CU_TRY(c, cudaMemcpyAsync(L.d_lut, lut, lb, cudaMemcpyDefault, c->stream));
+    }
     CU_TRY(c, cudaMemcpyAsync(L.d_bias, bias, bb, cudaMemcpyDefault, c->stream));
     CU_TRY(c, cudaStreamSynchronize(c->stream));
     L.plan = lutamm_plan{};

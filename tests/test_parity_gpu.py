@@ -161,12 +161,20 @@ def test_against_the_reference_operator(ctx, name):
     c = synth.make_case(M=M, K=CB * v, N=N, v=v, CT=CT, seed=77, scale=scale, lut_bias=lut_bias, reference_style=True)
     r = oracle.ref_amm_case(name, scale=scale, lut_bias=lut_bias)
     try:
-        ref_tiled = r.run_tiled(c.x, c.centroid, r.dpu_lut(c.lut), c.bias)
+        dpu_lut = r.dpu_lut(c.lut)
+        ref_tiled = r.run_tiled(c.x, c.centroid, dpu_lut, c.bias)
         where = r._where
     finally:
         r.close()
     ip, lp = P.make_params(M, CB * v, N, CB, CT, scale, lut_bias, n_stile=cfg["n_stile"], f_stile=cfg["f_stile"],
-                           n_mtile=cfg["n_mtile"], f_mtile=cfg["f_mtile"], cb_mtile=cfg["cb_mtile"])
+                           n_mtile=cfg["n_mtile"], f_mtile=cfg["f_mtile"], cb_mtile=cfg["cb_mtile"],
+                           lut_load_type=cfg["load_type"], f_load=cfg["f_load"], cb_load=cfg["cb_load"])
+    # the reference's own data contract: the LUT as reorder_pim_lut() leaves it, the DPU-tiled output
+    ctx.load_weights(8, c.centroid, dpu_lut, c.bias, scale, lut_bias, ip, lp, lut_layout=P.LUT_DPU_TILED)
+    y = np.zeros(M * N, dtype=np.float32)
+    ctx.amm_host(8, c.x, y, n_tokens=M, flags=P.FLAG_OUTPUT_TILED)
+    assert np.array_equal(y.view(np.uint32), ref_tiled.view(np.uint32)), "reference buffers in, reference bytes out"
+    ctx.unload_weights(8)
     ctx.load_weights(6, c.centroid, c.lut, c.bias, scale, lut_bias, ip, lp)
     for pname, plan in variants_for(CT, N, CB):
         ctx.set_plan(6, **plan)
