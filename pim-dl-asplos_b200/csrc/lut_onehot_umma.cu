@@ -333,10 +333,6 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
                     if (i + b >= it.nslab) continue;  // an odd last batch
                     const uint32_t slab = it.slab_begin + i + b;
                     const uint32_t x = ga + i + b, k = x & sa_mask, pa = (x >> sa_log2) & 1u;
-                    // the whole warp polls (one broadcast access), so it stays converged
-                    ok = ok && mbar_wait(a_empty0 + 8 * k, pa ^ 1, s_abort);
-                    if (!ok) continue;
-                    if constexpr (A_TMEM) tc_fence_after_sync();
                     // Row of the one-hot table per 16-byte chunk, then one conflict-free 16-byte load each.
                     // An index that is out of range for its chunk selects the all-zero row (the indices
                     // may come from a caller, not only from the search kernel).
@@ -366,7 +362,13 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
                             chunk[j] = *reinterpret_cast<const uint4*>(tab_lane + ((ix >> 4) == sub ? (ix & 15u) : 16u) * 128);
                         }
                     }
+                    // The row is in registers before the slot is waited for: what follows the wait is on
+                    // the slot's turn-around path.  The whole warp polls (one broadcast access), so it
+                    // stays converged.
+                    ok = ok && mbar_wait(a_empty0 + 8 * k, pa ^ 1, s_abort);
+                    if (!ok) continue;
                     if constexpr (A_TMEM) {
+                        tc_fence_after_sync();
                         // the row goes to this warp's lane quadrant of tensor memory, K bytes in column order
                         uint32_t w[32];
 #pragma unroll
