@@ -13,21 +13,24 @@
 // Persistent kernel: one CTA per SM walks a list of work items, an item being one
 // 128-token x N_TILE-column output tile, or one slice of its contraction axis when
 // split > 1 (each slice then writes its int32 partial tile to scratch in L2 with plain
-// stores, and the CTA that arrives last at a tile sums the slices and dequantises).
+// stores, and the CTAs holding a tile's slices sum it together and dequantise).
 // The accumulator is double-buffered in TMEM so the epilogue of one item overlaps the
-// main loop of the next.
+// main loop of the next.  Operands move through two rings of 128-byte slabs of the contraction
+// axis: LUT slabs in shared memory (as many as fit), one-hot slabs in tensor memory or shared
+// memory (what the accumulators, resp. the LUT ring, leave).
 //
 //   warp 0        TMA producer: B slabs = LUT^T[n0:n0+N_TILE][k:k+128] (K-major, 128-byte
 //                 swizzle) from the load-time transposed copy of the LUT
-//   warp 1        owns TMEM (alloc/dealloc); one lane issues tcgen05.mma, 4 per 128-byte slab
-//   warps 2-17    build the one-hot A slab in shared memory straight from the uint8 indices
-//                 (it never exists in HBM): four groups of four warps, group k taking every
-//                 fourth slab, one tile row per thread.  For CT = 16 one codebook is exactly
-//                 one 16-byte swizzle chunk, so a row is 8 vector stores.  Four groups because
-//                 a slab is a chain of latencies (index load, wait, proxy fence, arrive): they
-//                 have to overlap across slabs, not be shortened.
-//   warps 18-21   epilogue: TMEM -> registers -> shared-memory transpose -> dequantise ->
-//                 row-contiguous 16-byte global stores (each warp owns one 32-lane quadrant)
+//   warps 1-2     issue tcgen05.mma, 4 per slab, slab x by warp 1 + x % 2 (one elected lane);
+//                 warp 1 also owns TMEM (alloc/dealloc)
+//   warps 3-18    build the one-hot A slab straight from the uint8 indices (it never exists in
+//                 HBM): four groups of four warps, group k taking every fourth slab, one tile
+//                 row per thread, the row's eight 16-byte chunks read from a one-hot table in
+//                 shared memory.  Four groups because a slab is a chain of latencies (index
+//                 load, wait, fence, arrive): they have to overlap across slabs.
+//   warps 19-22   epilogue: TMEM -> registers -> shared-memory transpose -> dequantise ->
+//                 row-contiguous 16-byte global stores (each warp owns one 32-lane quadrant);
+//                 clears the accumulator behind itself
 //
 // HBM traffic: M*CB (indices) + CB*CT*N (LUT^T, once if L2-resident across M tiles)
 //              + 4*N (bias) + 4*M*N (output).
