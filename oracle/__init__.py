@@ -20,6 +20,11 @@ Two layers live here:
   the dequantisation of the restatement against the reference's own code
   (`RefAmm`, `build_ref_kernel`).
 
+* ``_ref/libref_amm_cpu.so`` - the reference's own CPU statement of the whole operator,
+  ``amm_cpu()`` of ``inference-engine/test/test_amm.cpp`` (that file compiled unmodified,
+  its ``main`` renamed): the second opinion on the restatement and the timed CPU baseline
+  (`ref_amm_cpu`).
+
 A third, numpy-only statement of the search (`numpy_index_calculation`) exists so the
 C restatement is cross-checked by an independent implementation on small cases.
 
@@ -41,6 +46,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB_PATH = os.path.join(_HERE, "liblutamm_oracle.so")
 _REF_PATH = os.path.join(_HERE, "_ref", "libref_index_calc.so")
 _REF_AMM_PATH = os.path.join(_HERE, "_ref", "libref_amm_host.so")
+_REF_AMM_CPU_PATH = os.path.join(_HERE, "_ref", "libref_amm_cpu.so")
 _REF_TREE = os.environ.get("LUTAMM_REFERENCE_DIR", "/root/reference")
 
 _u32 = ctypes.c_uint32
@@ -54,7 +60,8 @@ def build(force: bool = False) -> None:
     """Compile the C restatement (and the reference object when its tree is present)."""
     need = force or not os.path.exists(_LIB_PATH) or (
         os.path.getmtime(_LIB_PATH) < os.path.getmtime(os.path.join(_HERE, "lutamm_oracle.c")))
-    if need or (have_reference_tree() and not (os.path.exists(_REF_PATH) and os.path.exists(_REF_AMM_PATH))):
+    if need or (have_reference_tree() and not (os.path.exists(_REF_PATH) and os.path.exists(_REF_AMM_PATH)
+                                               and os.path.exists(_REF_AMM_CPU_PATH))):
         subprocess.run(["make", "-C", _HERE, "all", "REF=" + _REF_TREE], check=True, stdout=subprocess.DEVNULL)
     if have_reference_tree():
         build_ref_cases()
@@ -441,3 +448,36 @@ def build_lut(centroid, weight):
     else:
         lut = np.zeros((CB, CT, N), dtype=np.int8)
     return lut, np.float32(scale), np.float32(-scale * np.float32(0.0))
+
+
+# ---------------------------------------------------------------------------------------
+# The reference's own CPU AMM, amm_cpu() (test/test_amm.cpp:126-183), compiled unmodified.
+# ---------------------------------------------------------------------------------------
+def have_ref_amm_cpu() -> bool:
+    return os.path.exists(_REF_AMM_CPU_PATH)
+
+
+_ref_amm_cpu = None
+
+
+def ref_amm_cpu(x, centroid, lut, bias, scale: float, lut_bias: float = 0.0, nthreads: int | None = None) -> np.ndarray:
+    """Canonical tensors in, row-major [M][N] fp32 out.  Note that amm_cpu adds the LUT bias ONCE
+    (test_amm.cpp:181) where the production path adds it num_codebook times (pim_lut_host.cpp:201);
+    the two agree for lut_bias = 0, which converted weights always have."""
+    global _ref_amm_cpu
+    if _ref_amm_cpu is None:
+        R = ctypes.CDLL(_REF_AMM_CPU_PATH)
+        R.ref_amm_cpu.argtypes = [_fp, _fp, _i8p, _fp, _fp, ctypes.POINTER(RefIndexCalcParams), ctypes.POINTER(RefLUTParams)]
+        R.ref_amm_cpu.restype = None
+        _ref_amm_cpu = R
+    x, centroid, M, K, CB, CT, v = _chk(x, centroid)
+    lut = np.ascontiguousarray(lut, dtype=np.int8)
+    bias = np.ascontiguousarray(bias, dtype=np.float32)
+    N = lut.shape[2]
+    t = nthreads or default_threads()
+    ip = RefIndexCalcParams(M, K, v, CB, CT, t, max(M, 1), CB)
+    lp = RefLUTParams(M, N, CB, CT, scale, lut_bias, t, 1, 1, 1, N, max(M, 1), max(M, 1), N, CB, 0, N, CB)
+    out = np.empty((M, N), dtype=np.float32)
+    _ref_amm_cpu.ref_amm_cpu(_p(x, _fp), _p(centroid, _fp), _p(lut, _i8p), _p(bias, _fp), _p(out, _fp),
+                             ctypes.byref(ip), ctypes.byref(lp))
+    return out

@@ -105,3 +105,31 @@ def test_stand_in_rejects_a_short_read():
     assert L.dpu_launch(s, 0) != 0                                     # no program loaded
     L.dpu_free.argtypes = [Set]
     assert L.dpu_free(s) == 0
+
+
+needs_ref_cpu = pytest.mark.skipif(not oracle.have_ref_amm_cpu(), reason="oracle/_ref/libref_amm_cpu.so absent")
+
+
+@needs_ref_cpu
+@pytest.mark.parametrize("M,K,N,v,CT", [(64, 128, 96, 2, 16), (33, 96, 48, 4, 8), (17, 30, 16, 3, 5), (128, 256, 64, 8, 32)])
+def test_restatement_equals_reference_amm_cpu(M, K, N, v, CT):
+    """amm_cpu() of the reference's test_amm.cpp, compiled unmodified: the reference's own CPU path."""
+    c = synth.make_case(M=M, K=K, N=N, v=v, CT=CT, seed=M + N)
+    got = oracle.ref_amm_cpu(c.x, c.centroid, c.lut, c.bias, c.scale, 0.0, nthreads=4)
+    want, idx, acc = oracle.amm(c.x, c.centroid, c.lut, c.bias, c.scale, 0.0)
+    assert np.array_equal(bits(got), bits(want))
+    # with a LUT bias the reference's checker adds it once, the production path CB times: the known
+    # inconsistency, restated by dequant_checker_variant
+    got_b = oracle.ref_amm_cpu(c.x, c.centroid, c.lut, c.bias, c.scale, 0.2, nthreads=4)
+    assert np.array_equal(bits(got_b), bits(oracle.dequant_checker_variant(acc, c.bias, c.scale, 0.2)))
+
+
+@needs_ref_cpu
+@pytest.mark.parametrize("name", [n for n in golden_names() if n.startswith(("adversarial", "nonfinite", "normal_v2"))])
+def test_reference_amm_cpu_on_golden_vectors(name):
+    g = load_golden(name)
+    if float(g["lut_bias"]) != 0.0:
+        pytest.skip("checker variant differs by design when the LUT bias is not zero")
+    got = oracle.ref_amm_cpu(g["x"], g["centroid"], g["lut"], g["bias"], float(g["scale"]), 0.0, nthreads=2)
+    finite = np.isfinite(g["out"])
+    assert np.array_equal(bits(got)[finite], bits(g["out"])[finite])
