@@ -187,6 +187,50 @@ def test_against_the_reference_operator(ctx, name):
     ctx.unload_weights(6)
 
 
+def test_cpp_amm_host_with_the_reference_buffers(ctx):
+    """The C++ layer's amm_host_dpu_layout() - the reference's argument list AND data contract - called the
+    way transformer_layer.cpp calls amm_host(): parameter blocks by value, the re-tiled LUT, the DPU-tiled
+    output; bytes compared with the reference's own amm_host() on the UPMEM stand-in."""
+    import ctypes
+    import os
+    if not oracle.have_ref_amm():
+        pytest.skip("oracle/_ref (built from the reference tree) absent")
+    host = os.path.join(os.path.dirname(P.LIB_PATH), "libpimdl_host.so")
+    H = ctypes.CDLL(host)
+    name = "example_like"
+    cfg = oracle.REF_AMM_CASES[name]
+    M, N, CB, CT, v = (cfg[k] for k in ("M", "N", "CB", "CT", "v"))
+    c = synth.make_case(M=M, K=CB * v, N=N, v=v, CT=CT, seed=5, scale=0.1, lut_bias=0.2, reference_style=True)
+    r = oracle.ref_amm_case(name, scale=0.1, lut_bias=0.2)
+    try:
+        dpu_lut = r.dpu_lut(c.lut)
+        want = r.run_tiled(c.x, c.centroid, dpu_lut, c.bias)
+    finally:
+        r.close()
+    ip, lp = P.make_params(M, CB * v, N, CB, CT, 0.1, 0.2, n_stile=cfg["n_stile"], f_stile=cfg["f_stile"],
+                           n_mtile=cfg["n_mtile"], f_mtile=cfg["f_mtile"], cb_mtile=cfg["cb_mtile"],
+                           lut_load_type=cfg["load_type"], f_load=cfg["f_load"], cb_load=cfg["cb_load"])
+    fp = ctypes.POINTER(ctypes.c_float)
+    # C++ linkage, as the reference's amm_host has (Itanium-mangled names)
+    amm_host_dpu_layout = getattr(H, "_Z19amm_host_dpu_layoutP10lutamm_ctxPfS1_PaS1_S1_15IndexCalcParams9LUTParams")
+    amm_host_forget = getattr(H, "_Z15amm_host_forgetP10lutamm_ctx")
+    amm_host_dpu_layout.argtypes = [ctypes.c_void_p, fp, fp, ctypes.POINTER(ctypes.c_int8), fp, fp, P.IndexCalcParams, P.LUTParams]
+    amm_host_dpu_layout.restype = ctypes.c_int
+    amm_host_forget.argtypes = [ctypes.c_void_p]
+    amm_host_forget.restype = None
+    x = np.ascontiguousarray(c.x)
+    cen = np.ascontiguousarray(c.centroid)
+    bias = np.ascontiguousarray(c.bias)
+    out = np.zeros(M * N, dtype=np.float32)
+    as_f = lambda a: a.ctypes.data_as(fp)
+    for _ in range(2):   # the second call finds the weights resident
+        rc = amm_host_dpu_layout(ctx._h, as_f(x), as_f(cen), dpu_lut.ctypes.data_as(ctypes.POINTER(ctypes.c_int8)),
+                                   as_f(bias), as_f(out), ip, lp)
+        assert rc == 0, ctx._L.lutamm_last_error(ctx._h).decode()
+        assert np.array_equal(out.view(np.uint32), want.view(np.uint32))
+    amm_host_forget(ctx._h)
+
+
 def test_argument_validation(ctx):
     c = synth.make_case(M=4, K=32, N=16, v=2, CT=8, seed=1)
     with pytest.raises(P.LutAmmError) as e:
