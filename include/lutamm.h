@@ -95,7 +95,7 @@ typedef struct lutamm_plan {
     uint32_t variant;         /* LUTAMM_VARIANT_*                                         */
     uint32_t ccs_tokens;      /* tokens each search thread walks (0 = default)            */
     uint32_t gather_cfg;      /* gather kernel tile configuration id (0 = default)        */
-    uint32_t umma_n_tile;     /* tcgen05 N tile: 64, 128, 192 or 256 (0 = default)        */
+    uint32_t umma_n_tile;     /* tcgen05 N tile: 64, 128, 160, 192 or 256 (0 = default)   */
     uint32_t umma_split;      /* tcgen05 split of the codebook axis across CTAs (0 = auto) */
     uint32_t umma_stages;     /* tcgen05: LUT slabs in flight in shared memory (0 = as many as fit) */
     uint32_t umma_groups;     /* tcgen05 one-hot builder groups of 4 warps (0 = default)  */

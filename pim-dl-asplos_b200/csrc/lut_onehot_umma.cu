@@ -66,8 +66,8 @@ struct UmmaParams {
     uint32_t slabs_total;    // ceil(CB*CT / 128)
     uint32_t slabs_per_item; // ceil(slabs_total / split)
     uint32_t split;
-    uint32_t a_slots;        // ring of one-hot slabs (tensor memory or shared memory), a power of two
-    uint32_t a_slots_log2;
+    uint32_t a_slots;        // ring of one-hot slabs (tensor memory or shared memory)
+    uint32_t a_slots_magic;  // ceil(2^32 / a_slots): slab x lives in slot x % a_slots, found without a division
     uint32_t b_slots;        // ring of LUT slabs (shared memory), at least a_slots
     uint32_t tiles_m, tiles_n;
     uint32_t log2_ct;
@@ -94,6 +94,9 @@ __device__ __forceinline__ uint4 onehot16_bits(uint32_t n) {
                       shl32_clamped(1u, n - 96u));
 }
 __device__ __forceinline__ uint4 onehot16(uint32_t i) { return onehot16_bits(i < 16u ? i * 8u : 128u); }
+
+// x / d for x * d < 2^32, given magic = ceil(2^32 / d): one multiply-high.
+__device__ __forceinline__ uint32_t div_magic(uint32_t x, uint32_t magic) { return __umulhi(x, magic); }
 
 struct Item {
     uint32_t m0, n0, slab_begin, nslab, tile, z;
@@ -217,7 +220,8 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
         // loop measured 20 % slower), one elected lane issues.
         {
             const uint32_t me = warp - 1;
-            const uint32_t sa_mask = SA - 1, sa_log2 = p.a_slots_log2;
+            const uint32_t sa_magic = p.a_slots_magic;
+            auto a_slot = [&](uint32_t x, uint32_t& k, uint32_t& pa) { const uint32_t q = div_magic(x, sa_magic); k = x - q * SA; pa = q & 1u; };
             uint32_t j = me % SB, pb = 0, t = 0, x0 = 0;  // LUT slot / phase of this warp's next slab; slabs before the item
             bool ok = true;
             const uint32_t b_lo0 = (uint32_t)umma_desc_k_sw128(smem_u32(s_b));
@@ -225,7 +229,9 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
             const uint32_t desc_hi = (uint32_t)(umma_desc_k_sw128(0) >> 32);
             // Whether a slab's two slots are full is asked one turn ahead: a barrier query is a round
             // trip of the order of a hundred cycles.
-            bool ready = mbar_test2(b_full0 + 8 * j, pb, a_full0 + 8 * (me & sa_mask), (me >> sa_log2) & 1u);
+            uint32_t k, pa;
+            a_slot(me, k, pa);
+            bool ready = mbar_test2(b_full0 + 8 * j, pb, a_full0 + 8 * k, pa);
             for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++t) {
                 const Item it = decode_item(p, item, N_TILE);
                 const uint32_t ab = t & 1, aph = (t >> 1) & 1;
@@ -234,15 +240,17 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + ab * N_TILE;
                 for (uint32_t i = (x0 + me) & 1u; i < it.nslab; i += 2) {
-                    const uint32_t x = x0 + i, k = x & sa_mask, pa = (x >> sa_log2) & 1u;
+                    const uint32_t x = x0 + i;
+                    a_slot(x, k, pa);
                     if (!ready) {
                         ok = mbar_wait(b_full0 + 8 * j, pb, s_abort) && mbar_wait(a_full0 + 8 * k, pa, s_abort);
                         if (!ok) break;
                     }
                     uint32_t j2 = j + 2, pb2 = pb;
                     if (j2 >= SB) { j2 -= SB; pb2 ^= 1; }
-                    const uint32_t x2 = x + 2;
-                    const bool next_ready = mbar_test2(b_full0 + 8 * j2, pb2, a_full0 + 8 * (x2 & sa_mask), (x2 >> sa_log2) & 1u);
+                    uint32_t k2, pa2;
+                    a_slot(x + 2, k2, pa2);
+                    const bool next_ready = mbar_test2(b_full0 + 8 * j2, pb2, a_full0 + 8 * k2, pa2);
                     tc_fence_after_sync();
                     if (elect_one()) {
                         // descriptors differ from slot 0's only in the 16-byte-unit address field
@@ -300,12 +308,12 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
         // A group takes SPS consecutive slabs per turn: the fixed cost of a turn - the fences, the
         // arrival, the loop itself, a chain of latencies of many hundred cycles for a lone warp - is
         // then paid once per batch.  Batch q of the CTA's sequence goes to group q % groups; slab x of
-        // the sequence uses one-hot slot x % SA (SA is a power of two).
+        // the sequence uses one-hot slot x % SA.
         constexpr uint32_t kBatch = SPS;
         // Index bytes are fetched kPrefetch turns ahead: with the LUT tiles streaming through the same
         // L2 a load takes a good part of a turn.
         constexpr uint32_t kPrefetch = 2;
-        const uint32_t sa_mask = SA - 1, sa_log2 = p.a_slots_log2;
+        const uint32_t sa_magic = p.a_slots_magic;
         uint32_t ga = 0, qb = 0;  // slabs and batches of the CTA before the current item
         bool ok = true;
         for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
@@ -335,7 +343,7 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
                 for (uint32_t b = 0; b < kBatch; ++b) {
                     if (i + b >= it.nslab) continue;  // an odd last batch
                     const uint32_t slab = it.slab_begin + i + b;
-                    const uint32_t x = ga + i + b, k = x & sa_mask, pa = (x >> sa_log2) & 1u;
+                    const uint32_t x = ga + i + b, xq = div_magic(x, sa_magic), k = x - xq * SA, pa = xq & 1u;
                     // Row of the one-hot table per 16-byte chunk, then one conflict-free 16-byte load each.
                     // An index that is out of range for its chunk selects the all-zero row (the indices
                     // may come from a caller, not only from the search kernel).
@@ -396,7 +404,10 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
                 if (lane == 0 && ok) {
 #pragma unroll
                     for (uint32_t b = 0; b < kBatch; ++b)
-                        if (i + b < it.nslab) mbar_arrive(a_full0 + 8 * ((ga + i + b) & sa_mask));
+                        if (i + b < it.nslab) {
+                            const uint32_t x = ga + i + b;
+                            mbar_arrive(a_full0 + 8 * (x - div_magic(x, sa_magic) * SA));
+                        }
                 }
             }
             ga += it.nslab;
@@ -624,26 +635,26 @@ cudaError_t run(const CUtensorMap& map, const UmmaParams& p, uint32_t grid, size
     return cudaLaunchKernelEx(&cfg, k, map, p);
 }
 
-// Ring depths.  One-hot slots: a power of two (the builders address them by mask); in tensor memory
-// what the two accumulators leave of the 512 columns, 32 columns a slab; in shared memory as many as
-// leave the LUT ring at least as deep.  LUT slots: whatever shared memory still holds.
+// Ring depths.  One-hot slots: an even number (two warps issue alternate slabs); in tensor memory what the
+// two accumulators leave of the 512 columns, 32 columns a slab; in shared memory as many as leave the
+// LUT ring at least as deep.  LUT slots: whatever shared memory still holds.
 void ring_depths(uint32_t n_tile, bool a_tmem, uint32_t want_b, uint32_t* a_slots, uint32_t* b_slots) {
     uint32_t sa = kMaxASlots;
     if (a_tmem) {
         const uint32_t room = (512u - 2 * n_tile) / 32u;
-        while (sa > room) sa >>= 1;
+        if (sa > room) sa = room & ~1u;
     } else {
-        while (sa > 1 && umma_smem_bytes(n_tile, sa, sa, false) > kSmemLimit) sa >>= 1;
+        while (sa > 2 && umma_smem_bytes(n_tile, sa, sa, false) > kSmemLimit) sa -= 2;
     }
     uint32_t sb = kMaxBSlots;
     while (sb > sa && umma_smem_bytes(n_tile, sa, sb, a_tmem) > kSmemLimit) --sb;
     if (want_b && want_b < sb) sb = want_b < 2 ? 2 : want_b;
-    if (sa > sb) sa = sb >= 8 ? 8 : sb >= 4 ? 4 : sb >= 2 ? 2 : 1;
+    if (sa > sb) sa = sb & ~1u;
     *a_slots = sa;
     *b_slots = sb;
 }
 bool tile_ok(uint32_t n_tile, bool a_tmem) {
-    if (a_tmem) return n_tile == 64 || n_tile == 128 || n_tile == 192;
+    if (a_tmem) return n_tile == 64 || n_tile == 128 || n_tile == 160 || n_tile == 192;
     return n_tile == 64 || n_tile == 128 || n_tile == 256;
 }
 
@@ -706,7 +717,7 @@ cudaError_t umma_make_tmap(CUtensorMap* out, const int8_t* lut_t, uint32_t CB, u
                            uint32_t n_tile, const char** why) {
     *why = nullptr;
     if (!umma_supported(CB, CT, N)) { *why = "tcgen05 variant: needs num_centroid in {8,16,32,64,128,256}, num_codebook % 16 == 0, N % 16 == 0"; return cudaErrorInvalidValue; }
-    if (n_tile != 64 && n_tile != 128 && n_tile != 192 && n_tile != 256) { *why = "tcgen05 variant: N tile must be 64, 128, 192 or 256"; return cudaErrorInvalidValue; }
+    if (n_tile != 64 && n_tile != 128 && n_tile != 160 && n_tile != 192 && n_tile != 256) { *why = "tcgen05 variant: N tile must be 64, 128, 160, 192 or 256"; return cudaErrorInvalidValue; }
     EncodeTiledFn enc = get_encode_tiled();
     if (!enc) { *why = "cuTensorMapEncodeTiled is not available from this driver"; return cudaErrorNotSupported; }
     const uint64_t Kg = (uint64_t)CB * CT;
@@ -741,8 +752,7 @@ cudaError_t launch_umma(const LutArgs& a, const CUtensorMap& lut_t_map, const Um
     p.split = split;
     ring_depths(plan.n_tile, a_tmem, plan.stages, &p.a_slots, &p.b_slots);
     if (p.a_slots < 2 || p.b_slots < 2) { *why = "tcgen05 variant: this tile leaves room for fewer than two slabs in flight"; return cudaErrorInvalidValue; }
-    p.a_slots_log2 = 0;
-    while ((1u << p.a_slots_log2) < p.a_slots) ++p.a_slots_log2;
+    p.a_slots_magic = (uint32_t)(((1ull << 32) + p.a_slots - 1) / p.a_slots);
     // slabs a builder group takes per turn
     uint32_t sps = plan.sps >= 2 ? 2u : 1u;  // one measured at least as fast as two on every benchmark shape
     if (sps > p.a_slots / 2) sps = 1;
@@ -769,6 +779,7 @@ cudaError_t launch_umma(const LutArgs& a, const CUtensorMap& lut_t_map, const Um
     LUTAMM_UMMA_CASE(64, true, 2)
     LUTAMM_UMMA_CASE(128, true, 1)
     LUTAMM_UMMA_CASE(128, true, 2)
+    LUTAMM_UMMA_CASE(160, true, 1)
     LUTAMM_UMMA_CASE(192, true, 1)
     LUTAMM_UMMA_CASE(192, true, 2)
     LUTAMM_UMMA_CASE(64, false, 1)

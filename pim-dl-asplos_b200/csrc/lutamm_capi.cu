@@ -35,8 +35,8 @@ EncodeTiledFn get_encode_tiled() {
 
 namespace {
 
-constexpr int kNumUmmaTiles = 4;  // 64, 128, 192, 256
-inline int umma_tile_slot(uint32_t n_tile) { return n_tile == 64 ? 0 : n_tile == 128 ? 1 : n_tile == 192 ? 2 : 3; }
+constexpr int kNumUmmaTiles = 5;  // 64, 128, 160, 192, 256
+inline int umma_tile_slot(uint32_t n_tile) { return n_tile == 64 ? 0 : n_tile == 128 ? 1 : n_tile == 160 ? 2 : n_tile == 192 ? 3 : 4; }
 
 struct Layer {
     lutamm_index_params ip{};
@@ -50,7 +50,7 @@ struct Layer {
     std::vector<CUtensorMap> gather_maps;
     std::vector<char> gather_map_ok;
     CUtensorMap umma_maps[kNumUmmaTiles];
-    bool umma_map_ok[kNumUmmaTiles] = {false, false, false, false};
+    bool umma_map_ok[kNumUmmaTiles] = {false, false, false, false, false};
 };
 
 struct Buf {
@@ -209,7 +209,7 @@ int run_lut(lutamm_ctx* c, Layer& L, const uint8_t* d_idx, float* d_out, int32_t
         if (plan.umma_sps) up.sps = plan.umma_sps;
         if (!umma_tile_ok(up.n_tile, a_tmem))
             return fail(c, LUTAMM_EINVAL, "umma_n_tile must be 64, 128 or 256 with the one-hot operand in shared memory, "
-                                          "64, 128 or 192 with it in tensor memory");
+                                          "64, 128, 160 or 192 with it in tensor memory");
         if (!L.d_lut_t) {
             const size_t bytes = (size_t)L.CB * L.CT * L.N;
             CU_TRY(c, cudaMalloc(&L.d_lut_t, bytes));
@@ -680,7 +680,7 @@ int lutamm_set_plan(lutamm_ctx* c, int layer_id, const lutamm_plan* plan) {
     if (plan->umma_operand > 2) return fail(c, LUTAMM_EINVAL, "umma_operand must be 0, 1 (shared memory) or 2 (tensor memory)");
     if (plan->umma_n_tile && plan->umma_operand && !umma_tile_ok(plan->umma_n_tile, plan->umma_operand == 2))
         return fail(c, LUTAMM_EINVAL, "umma_n_tile must be 0, 64, 128 or 256 with the one-hot operand in shared memory, "
-                                      "0, 64, 128 or 192 with it in tensor memory");
+                                      "0, 64, 128, 160 or 192 with it in tensor memory");
     if (plan->umma_sps != 0 && plan->umma_sps != 1 && plan->umma_sps != 2 && plan->umma_sps != 4)
         return fail(c, LUTAMM_EINVAL, "umma_sps must be 0, 1, 2 or 4");
     if (plan->variant == LUTAMM_VARIANT_UMMA && !umma_supported(L->CB, L->CT, L->N))

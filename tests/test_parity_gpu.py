@@ -23,6 +23,8 @@ def variants_for(CT, N, CB=16):
               ("umma_ss256", dict(variant=U, umma_operand=1, umma_n_tile=256, umma_split=1, umma_sps=1)),
               ("umma_ss64s", dict(variant=U, umma_operand=1, umma_n_tile=64, umma_split=2)),
               ("umma_ts192", dict(variant=U, umma_operand=2, umma_n_tile=192, umma_split=1)),
+              ("umma_ts160", dict(variant=U, umma_operand=2, umma_n_tile=160, umma_split=1)),
+              ("umma_ts160s", dict(variant=U, umma_operand=2, umma_n_tile=160, umma_split=2, umma_groups=3)),
               ("umma_ts128s", dict(variant=U, umma_operand=2, umma_n_tile=128, umma_split=3, umma_sps=4)),
               ("umma_ts64", dict(variant=U, umma_operand=2, umma_n_tile=64, umma_split=1, umma_groups=2, umma_sps=4)),
               ("umma_ts192_1", dict(variant=U, umma_operand=2, umma_n_tile=192, umma_split=2, umma_sps=1, umma_groups=3)),
