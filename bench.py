@@ -70,6 +70,13 @@ def peaks():
     return FALLBACK_HBM_GBS, "fallback"
 
 
+def measured_bf16_tflops():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        return float(json.load(open(p)).get("bf16_tflops", 0.0)) or None
+    return 1590.0  # the pool's earlier measurement, used when the file is absent
+
+
 def recorded_traffic(workload: str):
     """DRAM bytes per step of the dominant kernel from the committed ncu capture, if any."""
     p = os.path.join(ROOT, "profiles", "traffic.json")
@@ -352,6 +359,14 @@ def run_ours(args):
                 "search_kernel_ms_per_step": ccs_ms,
                 "search_algorithmic_bytes_per_step": sum(a["ccs"] for a in alg),
                 "whole_step_frac": (sum(a["total"] for a in alg) / (ms_per_step * 1e-3) / 1e9) / peak}
+    # the same launches seen as what they are on the default plan, an int8 one-hot contraction on the
+    # tensor pipe: 2*M*N*CB*CT operations; against twice the measured dense bf16 rate (the int8 rate is
+    # not in MEASURED_PEAKS.json; nominally it is twice bf16's)
+    ops = sum(2.0 * M * L["n_loc"] * (L["K"] // v) * CT for L in layers)
+    bf16 = measured_bf16_tflops()
+    roofline["tensor_view"] = {"int8_tops": ops / (lut_ms * 1e-3) / 1e12,
+                               "assumed_int8_peak_tops": 2.0 * bf16 if bf16 else None,
+                               "frac": (ops / (lut_ms * 1e-3) / 1e12) / (2.0 * bf16) if bf16 else None}
 
     # ---- end to end: pinned host buffers through the public call, copies inside the timing
     e2e = None
