@@ -696,8 +696,12 @@ void umma_default_plan(uint32_t M, uint32_t CB, uint32_t CT, uint32_t N, int sm_
     auto tiles_for = [&](uint32_t nt) { return tm * ((N + nt - 1) / nt); };
     bool a_tmem;
     if (operand == 0 && n_tile == 0) {
-        if (N >= 192 && tiles_for(192) >= (uint32_t)sm_count) { a_tmem = true; n_tile = 192; }
-        else { a_tmem = true; n_tile = N > 64 ? 128 : 64; }
+        const uint32_t sms = (uint32_t)sm_count;
+        a_tmem = true;
+        if (N >= 192 && tiles_for(192) >= sms) n_tile = 192;
+        // 128-wide tiles would need a second, mostly empty round while 192-wide ones fill most SMs once
+        else if (N >= 192 && tiles_for(128) > sms && 4 * tiles_for(192) >= 3 * sms) n_tile = 192;
+        else n_tile = N > 64 ? 128 : 64;
     } else if (operand == 0) {
         a_tmem = n_tile != 256;
     } else {
