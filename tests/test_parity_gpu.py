@@ -233,6 +233,30 @@ def test_cpp_amm_host_with_the_reference_buffers(ctx):
     amm_host_forget(ctx._h)
 
 
+@pytest.mark.parametrize("M,K,N", [(1024, 768, 768), (1000, 512, 400), (2304, 256, 1536)])
+def test_back_to_back_async_calls_stay_bit_identical(ctx, M, K, N):
+    """Many asynchronous calls queued back to back (programmatic dependent launch overlaps each kernel's
+    prologue with its predecessor; split-K tiles are summed by several CTAs that wait for one another):
+    every output equals the oracle's, bit for bit, for every plan."""
+    import torch
+    v, CT = 2, 16
+    c = synth.make_case(M=M, K=K, N=N, v=v, CT=CT, seed=M)
+    want = torch.from_numpy(oracle.amm(c.x, c.centroid, c.lut, c.bias, c.scale, 0.0)[0]).cuda()
+    ctx.load_weights(2, c.centroid, c.lut, c.bias, c.scale)
+    x = torch.from_numpy(c.x).cuda()
+    for plan in (dict(variant=P.VARIANT_AUTO), dict(variant=P.VARIANT_UMMA, umma_split=2),
+                 dict(variant=P.VARIANT_UMMA, umma_split=5, umma_n_tile=64), dict(variant=P.VARIANT_UMMA, umma_operand=1),
+                 dict(variant=P.VARIANT_GATHER)):
+        ctx.set_plan(2, **plan)
+        ys = [torch.empty(M, N, device="cuda") for _ in range(3)]
+        for it in range(60):
+            ctx.amm_host(2, x, ys[it % 3], flags=P.FLAG_ASYNC)
+        ctx.sync()
+        for y in ys:
+            assert torch.equal(y.view(torch.int32), want.view(torch.int32)), plan
+    ctx.unload_weights(2)
+
+
 def test_argument_validation(ctx):
     c = synth.make_case(M=4, K=32, N=16, v=2, CT=8, seed=1)
     with pytest.raises(P.LutAmmError) as e:
