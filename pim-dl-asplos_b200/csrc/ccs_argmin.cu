@@ -70,6 +70,11 @@ ccs_reg_kernel(const float* __restrict__ x, const float* __restrict__ cent, void
     // set-up, tensor-memory allocation, the first LUT tiles - while the search runs; it
     // waits for this grid to finish before it touches the indices.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // This kernel is itself launched as a programmatic dependent of whatever precedes it in the stream
+    // (so that its launch latency overlaps that kernel's tail): everything it reads or overwrites - the
+    // activations, the index buffer the previous LUT kernel may still be reading - comes after this wait,
+    // which returns once the preceding grid has completed and its writes are visible.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t cb = blockIdx.x * kRegThreads + threadIdx.x;
     const bool active = cb < CB;
     const uint32_t m0 = blockIdx.y * tokens_per_cta;
@@ -176,6 +181,7 @@ ccs_smem_kernel(const float* __restrict__ x, const float* __restrict__ cent, voi
                 uint32_t cb_mtile) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // see ccs_reg_kernel
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t v = V > 0 ? (uint32_t)V : v_rt;
     float* s_cent = reinterpret_cast<float*>(smem_raw);                   // [cbs][CT][v]
     const uint32_t cb0 = blockIdx.x * cb_per_cta;
@@ -240,6 +246,24 @@ ccs_smem_kernel(const float* __restrict__ x, const float* __restrict__ cent, voi
     }
 }
 
+// Launch with programmatic stream serialisation allowed: the grid may be scheduled while the preceding
+// kernel of the stream is still running; the kernels above wait for it (griddepcontrol.wait) before they
+// touch memory, so the ordering is that of a plain launch and only the launch latency overlaps.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_dependent(void (*k)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, k, static_cast<KArgs>(args)...);
+}
+
 template <int V, int CT, int kTok>
 cudaError_t run_reg_tok(const CcsArgs& a, cudaStream_t s) {
     // Default run length per thread: long enough to amortise the centroid load, short enough
@@ -255,12 +279,10 @@ cudaError_t run_reg_tok(const CcsArgs& a, cudaStream_t s) {
     tpt = (tpt + kTok - 1) / kTok * kTok;
     dim3 grid((a.CB + kRegThreads - 1) / kRegThreads, (a.M + tpt - 1) / tpt);
     if (a.format == LUTAMM_INDEX_U16_TILED)
-        ccs_reg_kernel<V, CT, true, kTok><<<grid, kRegThreads, 0, s>>>(a.x, a.centroid, a.idx_out, a.M, a.K, a.CB, tpt,
-                                                                         a.n_stile, a.cb_mtile);
-    else
-        ccs_reg_kernel<V, CT, false, kTok><<<grid, kRegThreads, 0, s>>>(a.x, a.centroid, a.idx_out, a.M, a.K, a.CB, tpt,
-                                                                          a.n_stile, a.cb_mtile);
-    return cudaGetLastError();
+        return launch_dependent(ccs_reg_kernel<V, CT, true, kTok>, grid, dim3(kRegThreads), 0, s, a.x, a.centroid, a.idx_out,
+                                a.M, a.K, a.CB, tpt, a.n_stile, a.cb_mtile);
+    return launch_dependent(ccs_reg_kernel<V, CT, false, kTok>, grid, dim3(kRegThreads), 0, s, a.x, a.centroid, a.idx_out,
+                            a.M, a.K, a.CB, tpt, a.n_stile, a.cb_mtile);
 }
 
 template <int V, int CT>
@@ -286,16 +308,15 @@ cudaError_t run_smem(const CcsArgs& a, cudaStream_t s) {
         auto k = ccs_smem_kernel<V, true>;
         e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
-        k<<<grid, kSmemThreads, smem, s>>>(a.x, a.centroid, a.idx_out, a.M, a.K, a.v, a.CB, a.CT, cb_per_cta,
-                                           a.n_stile, a.cb_mtile);
+        return launch_dependent(k, grid, dim3(kSmemThreads), smem, s, a.x, a.centroid, a.idx_out, a.M, a.K, a.v, a.CB, a.CT,
+                                cb_per_cta, a.n_stile, a.cb_mtile);
     } else {
         auto k = ccs_smem_kernel<V, false>;
         e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
-        k<<<grid, kSmemThreads, smem, s>>>(a.x, a.centroid, a.idx_out, a.M, a.K, a.v, a.CB, a.CT, cb_per_cta,
-                                           a.n_stile, a.cb_mtile);
+        return launch_dependent(k, grid, dim3(kSmemThreads), smem, s, a.x, a.centroid, a.idx_out, a.M, a.K, a.v, a.CB, a.CT,
+                                cb_per_cta, a.n_stile, a.cb_mtile);
     }
-    return cudaGetLastError();
 }
 
 }  // namespace
