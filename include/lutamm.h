@@ -206,6 +206,20 @@ int lutamm_pim_lut(lutamm_ctx* ctx, int layer_id, const uint8_t* index, float* o
 int lutamm_set_plan(lutamm_ctx* ctx, int layer_id, const lutamm_plan* plan);
 int lutamm_get_plan(lutamm_ctx* ctx, int layer_id, lutamm_plan* plan);
 
+/* Activation applied to every output element after the dequantisation, inside the LUT kernel's
+ * epilogue (the int32 accumulators lutamm_amm_debug returns are not affected).  In the reference the
+ * FFN1 operator is followed by a separate in-place GELU pass over its output
+ * (src/host/transformer_layer.cpp:503, ggml_gelu_inplace); fused here it costs no memory traffic.
+ *   LUTAMM_ACT_GELU_TANH       0.5 x (1 + tanh(u)), u = sqrt(2/pi) x (1 + 0.044715 x^2), in fp32, evaluated in the
+ *                              cancellation-free form x / (1 + exp(-2u)); relative error below 1e-6
+ *   LUTAMM_ACT_GELU_TANH_F16   the same with x rounded to fp16 first and the result rounded to fp16, the
+ *                              precision of ggml's table-driven GELU (one table entry per fp16 value)
+ * The default after lutamm_load_weights is LUTAMM_ACT_NONE. */
+#define LUTAMM_ACT_NONE           0u
+#define LUTAMM_ACT_GELU_TANH      1u
+#define LUTAMM_ACT_GELU_TANH_F16  2u
+int lutamm_set_activation(lutamm_ctx* ctx, int layer_id, uint32_t activation);
+
 /* Replaces the auto-tuner's mapping search (src/tuner/auto_tuner.cpp:368-603): times the
  * candidate kernel variants and tile configurations for n_tokens rows with CUDA events
  * and installs the fastest.  best may be NULL. */

@@ -220,6 +220,24 @@ def amm(x, centroid, lut, bias, scale: float, lut_bias: float = 0.0, nthreads: i
     return out, idx, acc
 
 
+def gelu_tanh(y: np.ndarray, through_f16: bool = False) -> np.ndarray:
+    """Checker for the activation the library can fuse after the dequantisation.  The reference
+    applies GELU to the FFN1 output as a separate pass (inference-engine/src/host/transformer_layer.cpp:503,
+    ggml_gelu_inplace).  ggml is an un-vendored submodule without a recoverable commit, so this follows
+    its published definition instead of its source - 0.5 x (1 + tanh(sqrt(2/pi) x (1 + 0.044715 x^2))),
+    evaluated per fp16 value through a table when `through_f16` (input rounded to fp16, result rounded to
+    fp16) - and is evaluated in float64 here: parity unpinned, compared within a stated tolerance."""
+    x = np.asarray(y, dtype=np.float32)
+    if through_f16:
+        x = x.astype(np.float16).astype(np.float32)
+    xd = x.astype(np.float64)
+    g = 0.5 * xd * (1.0 + np.tanh(np.sqrt(2.0 / np.pi) * xd * (1.0 + 0.044715 * xd * xd)))
+    g = g.astype(np.float32)
+    if through_f16:
+        g = g.astype(np.float16).astype(np.float32)
+    return g
+
+
 def tiled_output_offset(i: int, j: int, n_stile: int, f_stile: int, f_mtile: int, lut_parallelism: int) -> int:
     return int(lib().oracle_tiled_output_offset(i, j, n_stile, f_stile, f_mtile, lut_parallelism))
 

@@ -22,12 +22,13 @@ FLAG_ASYNC, FLAG_OUTPUT_TILED = 1, 2
 VARIANT_AUTO, VARIANT_GATHER, VARIANT_UMMA = 0, 1, 2
 INDEX_U8_ROWMAJOR, INDEX_U16_TILED = 0, 1
 LUT_CANONICAL, LUT_DPU_TILED = 0, 1
+ACT_NONE, ACT_GELU_TANH, ACT_GELU_TANH_F16 = 0, 1, 2
 
 # every symbol include/lutamm.h declares
 ABI_SYMBOLS = [
     "lutamm_create", "lutamm_destroy", "lutamm_set_stream", "lutamm_sync", "lutamm_last_error",
     "lutamm_version", "lutamm_load_weights", "lutamm_unload_weights", "lutamm_amm", "lutamm_amm_debug",
-    "lutamm_index_calculation", "lutamm_pim_lut", "lutamm_set_plan", "lutamm_get_plan", "lutamm_tune",
+    "lutamm_index_calculation", "lutamm_pim_lut", "lutamm_set_plan", "lutamm_get_plan", "lutamm_set_activation", "lutamm_tune",
     "lutamm_enable_timing", "lutamm_get_timings", "lutamm_launch_count",
     "lutamm_amm_static_scratch", "lutamm_static_scratch_last_error", "lutamm_build_lut",
     "lutamm_load_weights_layout",
@@ -111,6 +112,7 @@ def load_library() -> ctypes.CDLL:
     L.lutamm_pim_lut.argtypes = [vp, i32, vp, vp, u32, u32]
     L.lutamm_set_plan.argtypes = [vp, i32, ctypes.POINTER(Plan)]
     L.lutamm_get_plan.argtypes = [vp, i32, ctypes.POINTER(Plan)]
+    L.lutamm_set_activation.argtypes = [vp, i32, u32]
     L.lutamm_tune.argtypes = [vp, i32, u32, ctypes.POINTER(Plan)]
     L.lutamm_enable_timing.argtypes = [vp, i32]
     L.lutamm_get_timings.argtypes = [vp, ctypes.POINTER(Timings)]
@@ -290,6 +292,10 @@ class LutAmmContext:
         for k, v in kw.items():
             setattr(p, k, v)
         self._check(self._L.lutamm_set_plan(self._h, layer_id, ctypes.byref(p)))
+
+    def set_activation(self, layer_id: int, activation: int):
+        """Activation fused into the LUT kernel's epilogue: ACT_NONE, ACT_GELU_TANH or ACT_GELU_TANH_F16."""
+        self._check(self._L.lutamm_set_activation(self._h, layer_id, activation))
 
     def get_plan(self, layer_id: int) -> dict:
         p = Plan()

@@ -33,6 +33,7 @@ struct LutArgs {
     uint32_t M, CB, CT, N;
     float scale, lut_bias;
     OutLayout layout;
+    uint32_t act;         // LUTAMM_ACT_*: applied after the dequantisation
 };
 
 // Gather variant: LUT canonical [CB][CT][N] staged by 3-D TMA tiles.

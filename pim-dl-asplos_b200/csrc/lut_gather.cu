@@ -208,6 +208,10 @@ lut_gather_kernel(const __grid_constant__ CUtensorMap lut_map, LutArgs a, uint32
             float o[COLS];
 #pragma unroll
             for (int k = 0; k < COLS; ++k) o[k] = dequant_one(acc[t][k], a.scale, lbcb, bias[k]);
+            if (a.act) {
+#pragma unroll
+                for (int k = 0; k < COLS; ++k) o[k] = activate_one(o[k], a.act);
+            }
             if (a.layout.tiled) {
 #pragma unroll
                 for (int k = 0; k < COLS; ++k) a.out[tiled_out_offset(m, n + k, a.layout)] = o[k];

@@ -71,7 +71,7 @@ struct UmmaParams {
     uint32_t b_slots;        // ring of LUT slabs (shared memory), at least a_slots
     uint32_t tiles_m, tiles_n;
     uint32_t log2_ct;
-    uint32_t groups;         // A-builder groups (1..6)
+    uint32_t groups;         // A-builder groups (1..4); a_slots % (groups * slabs per turn) == 0
     int32_t* acc_scratch;    // [split][M][N] int32 partial sums (split > 1); needs no initialisation
     uint32_t* tile_counters;
     uint32_t* dev_err;
@@ -491,6 +491,15 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
                                 o[k].z = dequant_one(val[k].z, a.scale, lbcb, b4.z);
                                 o[k].w = dequant_one(val[k].w, a.scale, lbcb, b4.w);
                             }
+                            if (a.act) {
+#pragma unroll
+                                for (uint32_t k = 0; k < 4; ++k) {
+                                    o[k].x = activate_one(o[k].x, a.act);
+                                    o[k].y = activate_one(o[k].y, a.act);
+                                    o[k].z = activate_one(o[k].z, a.act);
+                                    o[k].w = activate_one(o[k].w, a.act);
+                                }
+                            }
                             if (!a.layout.tiled) {
                                 float* orow = a.out + (size_t)m_half * a.N + n;
 #pragma unroll
@@ -571,8 +580,12 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
                             const uint32_t n = it.n0 + c * 32 + ch * 4;
                             if (n >= a.N) continue;
                             const float4 b4 = __ldg(reinterpret_cast<const float4*>(a.bias + n));
-                            const float o[4] = {dequant_one(val[c].x, a.scale, lbcb, b4.x), dequant_one(val[c].y, a.scale, lbcb, b4.y),
-                                                dequant_one(val[c].z, a.scale, lbcb, b4.z), dequant_one(val[c].w, a.scale, lbcb, b4.w)};
+                            float o[4] = {dequant_one(val[c].x, a.scale, lbcb, b4.x), dequant_one(val[c].y, a.scale, lbcb, b4.y),
+                                          dequant_one(val[c].z, a.scale, lbcb, b4.z), dequant_one(val[c].w, a.scale, lbcb, b4.w)};
+                            if (a.act) {
+#pragma unroll
+                                for (uint32_t k = 0; k < 4; ++k) o[k] = activate_one(o[k], a.act);
+                            }
                             if (!a.layout.tiled) {
                                 *reinterpret_cast<float4*>(a.out + (size_t)mm * a.N + n) = make_float4(o[0], o[1], o[2], o[3]);
                             } else {
@@ -649,7 +662,13 @@ void ring_depths(uint32_t n_tile, bool a_tmem, uint32_t want_b, uint32_t* a_slot
     uint32_t sb = kMaxBSlots;
     while (sb > sa && umma_smem_bytes(n_tile, sa, sb, a_tmem) > kSmemLimit) --sb;
     if (want_b && want_b < sb) sb = want_b < 2 ? 2 : want_b;
-    if (sa > sb) sa = sb & ~1u;
+    // Both rings hold an even number of slots: the two MMA-issuing warps take alternate slabs, so with an
+    // even ring every slot is always consumed by the same warp, whose program order then guarantees that
+    // a slot's previous use was waited for before the next one is asked about.  (An mbarrier parity wait
+    // tells only two consecutive phases apart: asked about use q while use q-1 is still outstanding, it
+    // answers for use q-2.)
+    sb &= ~1u;
+    if (sa > sb) sa = sb;
     *a_slots = sa;
     *b_slots = sb;
 }
@@ -759,7 +778,7 @@ cudaError_t launch_umma(const LutArgs& a, const CUtensorMap& lut_t_map, const Um
     p.a_slots_magic = (uint32_t)(((1ull << 32) + p.a_slots - 1) / p.a_slots);
     // slabs a builder group takes per turn
     uint32_t sps = plan.sps >= 2 ? 2u : 1u;  // one measured at least as fast as two on every benchmark shape
-    if (sps > p.a_slots / 2) sps = 1;
+    if (sps > p.a_slots / 2 || plan.n_tile == 160) sps = 1;  // (160-wide tiles are built for one slab per turn)
     p.tiles_m = (a.M + kMTile - 1) / kMTile;
     p.tiles_n = (a.N + plan.n_tile - 1) / plan.n_tile;
     p.log2_ct = 0;
@@ -767,16 +786,24 @@ cudaError_t launch_umma(const LutArgs& a, const CUtensorMap& lut_t_map, const Um
     p.acc_scratch = acc_scratch;
     p.tile_counters = tile_counters;
     p.dev_err = dev_err;
-    // A builder group may run at most one use of a slot ahead of the MMA warp (mbarrier parity only
-    // tells two consecutive phases apart), which holds iff groups * slabs per turn <= one-hot slots.
+    // Every one-hot slot must always be filled by the same builder group, so that the group's program
+    // order puts its wait for use q-1 of the slot before its wait for use q: an mbarrier parity wait tells
+    // only two consecutive phases apart, and groups do not wait for one another - with the slots rotating
+    // through the groups, one group two uses ahead of a stalled one would take the stalled group's
+    // still-pending phase for its own and overwrite a slab that was never consumed.  Slab x goes to group
+    // (x / sps) % groups and to slot x % slots, so the condition is slots % (groups * sps) == 0: take the
+    // largest such group count not above the one asked for.
     p.groups = plan.groups ? (plan.groups > kMaxAgenGroups ? kMaxAgenGroups : plan.groups) : 4;
-    if (p.groups > p.a_slots / sps) p.groups = p.a_slots / sps;
-    if (p.groups == 0) p.groups = 1;
-    if (split > 1 && (!acc_scratch || !tile_counters)) { *why = "tcgen05 variant: split > 1 needs scratch"; return cudaErrorInvalidValue; }
-    const size_t smem = umma_smem_bytes(plan.n_tile, p.a_slots, p.b_slots, a_tmem);
+    // Two-slab turns are counted per item, slots over the CTA's whole slab sequence: after an item with
+    // an odd number of slabs the pairs would straddle slots differently and the slots would change
+    // hands, so a CTA that takes several items of which any is odd builds one slab per turn.
     const uint64_t items = (uint64_t)p.tiles_m * p.tiles_n * split;
     const uint32_t cap = plan.max_ctas ? plan.max_ctas : 148u;
     const uint32_t grid = (uint32_t)(items < cap ? items : cap);
+    if (sps == 2 && items > grid && ((p.slabs_per_item & 1u) || (p.slabs_total & 1u))) sps = 1;
+    while (p.groups > 1 && p.a_slots % (p.groups * sps) != 0) --p.groups;
+    if (split > 1 && (!acc_scratch || !tile_counters)) { *why = "tcgen05 variant: split > 1 needs scratch"; return cudaErrorInvalidValue; }
+    const size_t smem = umma_smem_bytes(plan.n_tile, p.a_slots, p.b_slots, a_tmem);
 #define LUTAMM_UMMA_CASE(NT, TM, SP) \
     if (plan.n_tile == NT && a_tmem == TM && sps == SP) return run<NT, TM, SP>(lut_t_map, p, grid, smem, s);
     LUTAMM_UMMA_CASE(64, true, 1)

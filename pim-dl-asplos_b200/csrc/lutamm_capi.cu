@@ -47,6 +47,7 @@ struct Layer {
     int8_t* d_lut_t = nullptr;  // [N][CB*CT], made on first use of the tcgen05 variant
     float* d_bias = nullptr;
     lutamm_plan plan{};
+    uint32_t act = LUTAMM_ACT_NONE;
     std::vector<CUtensorMap> gather_maps;
     std::vector<char> gather_map_ok;
     CUtensorMap umma_maps[kNumUmmaTiles];
@@ -194,6 +195,7 @@ int run_lut(lutamm_ctx* c, Layer& L, const uint8_t* d_idx, float* d_out, int32_t
     a.scale = L.lp.scale;
     a.lut_bias = L.lp.bias;
     a.layout = make_layout(L, flags);
+    a.act = L.act;
     const char* why = nullptr;
     uint32_t variant = plan.variant;
     if (variant == LUTAMM_VARIANT_AUTO) variant = resolve_variant(c, L);
@@ -686,6 +688,15 @@ int lutamm_set_plan(lutamm_ctx* c, int layer_id, const lutamm_plan* plan) {
     if (plan->variant == LUTAMM_VARIANT_UMMA && !umma_supported(L->CB, L->CT, L->N))
         return fail(c, LUTAMM_EUNSUPPORTED, "tcgen05 variant does not cover this shape");
     L->plan = *plan;
+    return LUTAMM_OK;
+}
+
+int lutamm_set_activation(lutamm_ctx* c, int layer_id, uint32_t activation) {
+    if (!c) return fail(nullptr, LUTAMM_EINVAL, "null context");
+    Layer* L = find_layer(c, layer_id);
+    if (!L) return fail(c, LUTAMM_ENOLAYER, "no weights loaded for layer " + std::to_string(layer_id));
+    if (activation > LUTAMM_ACT_GELU_TANH_F16) return fail(c, LUTAMM_EINVAL, "unknown activation");
+    L->act = activation;
     return LUTAMM_OK;
 }
 

@@ -34,6 +34,8 @@ def parse_args():
     p.add_argument('--tune', action='store_true', default=False)
     p.add_argument('--model_weight_file', type=str, default=None)
     p.add_argument('--layers', type=int, default=None, help='override layer_num (run_layer: 1)')
+    p.add_argument('--separate_gelu', action='store_true', default=False,
+                   help='run GELU as its own pass after FFN1, as the reference does, instead of in the FFN1 epilogue')
     return p.parse_args()
 
 
@@ -73,7 +75,7 @@ def run(args, whole_model: bool):
                 cen, lut, bias, _, _ = w[name]
                 w[name] = (cen, lut, bias, cfg["scale"][name], cfg["lut_bias"][name])
             weights.append(w)
-    model = L.LutTransformer(ctx, weights, S, B, H, plans=cfg["plans"])
+    model = L.LutTransformer(ctx, weights, S, B, H, plans=cfg["plans"], fused_gelu=not getattr(args, "separate_gelu", False))
     if args.tune:
         plans = model.layers[0].tune()
         for lay in model.layers[1:]:

@@ -10,9 +10,11 @@ and transformer_inference() (transformer_model.cpp:13-49) of the reference:
     f     = GELU(AMM_ffn1(h))                    then the residual - not LayerNorm(x + o)
     y     = h + LayerNorm_2(AMM_ffn2(f))
 
-The four linears run in the CUDA library through the C ABI; attention, LayerNorm, GELU and
-the residual adds are plain PyTorch on the same stream (they stay dense fp32, as in the
-reference, where they run in ggml on the host).  All the loops of the reference that move
+The four linears run in the CUDA library through the C ABI; attention, LayerNorm and the
+residual adds are plain PyTorch on the same stream (they stay dense fp32, as in the
+reference, where they run in ggml on the host).  The GELU after FFN1 - a separate in-place
+pass in the reference (:503) - is applied inside the FFN1 operator's epilogue
+(`fused_gelu`, lutamm_set_activation), which saves one read and one write of [n, ffn_dim].  All the loops of the reference that move
 data between the DPU-tiled layout and row-major (:97-208, :449-471, :520-542, :574-596)
 have no counterpart: every tensor here is row-major.
 
@@ -24,7 +26,7 @@ from __future__ import annotations
 
 import numpy as np
 
-from . import FLAG_ASYNC, LutAmmContext, synth
+from . import ACT_GELU_TANH, FLAG_ASYNC, LutAmmContext, synth
 
 LINEARS = ("qkv", "o", "ffn1", "ffn2")
 
@@ -81,7 +83,7 @@ class LutTransformerLayer:
     """One encoder layer; `forward` takes and returns a device tensor [n, token_dim]."""
 
     def __init__(self, ctx: LutAmmContext, weights: dict, seq_len: int, batch_size: int, head_num: int,
-                 first_layer_id: int = 0, plans: dict | None = None):
+                 first_layer_id: int = 0, plans: dict | None = None, fused_gelu: bool = True):
         import torch
         self.ctx, self.torch = ctx, torch
         self.seq_len, self.batch, self.heads = seq_len, batch_size, head_num
@@ -94,6 +96,9 @@ class LutTransformerLayer:
             if plans and name in plans:
                 ctx.set_plan(lid, **plans[name])
             self.ids[name] = lid
+        self.fused_gelu = fused_gelu
+        if fused_gelu:
+            ctx.set_activation(self.ids["ffn1"], ACT_GELU_TANH)
         self.token_dim = weights["o"][1].shape[2]
         self.ffn_dim = weights["ffn1"][1].shape[2]
         dev = torch.device("cuda", ctx.device)
@@ -122,7 +127,9 @@ class LutTransformerLayer:
         att = att.transpose(1, 2).reshape(self.n, D).contiguous()
         o = self._amm("o", att)
         h = x + F.layer_norm(o, (D,), self.ln["ln1"][0], self.ln["ln1"][1], eps=1e-6)
-        f = F.gelu(self._amm("ffn1", h.contiguous()), approximate="tanh")
+        f = self._amm("ffn1", h.contiguous())
+        if not self.fused_gelu:
+            f = F.gelu(f, approximate="tanh")
         y = h + F.layer_norm(self._amm("ffn2", f), (D,), self.ln["ln2"][0], self.ln["ln2"][1], eps=1e-6)
         return y
 
@@ -130,8 +137,9 @@ class LutTransformerLayer:
 class LutTransformer:
     """layer_num encoder layers back to back (transformer_model.cpp:13-49)."""
 
-    def __init__(self, ctx, layer_weights: list, seq_len, batch_size, head_num, plans=None):
-        self.layers = [LutTransformerLayer(ctx, w, seq_len, batch_size, head_num, first_layer_id=4 * i, plans=plans)
+    def __init__(self, ctx, layer_weights: list, seq_len, batch_size, head_num, plans=None, fused_gelu=True):
+        self.layers = [LutTransformerLayer(ctx, w, seq_len, batch_size, head_num, first_layer_id=4 * i, plans=plans,
+                                           fused_gelu=fused_gelu)
                        for i, w in enumerate(layer_weights)]
 
     def forward(self, x):

@@ -121,3 +121,19 @@ def test_reorder_lut_roundtrip():
     lut = rng.integers(-128, 128, (CB, CT, N), dtype=np.int8)
     t = oracle.reorder_lut(lut, tile).reshape(N // tile, CB, CT, tile)
     assert np.array_equal(t.transpose(1, 2, 0, 3).reshape(CB, CT, N), lut)
+
+
+def test_gelu_checker_properties():
+    """The activation checker: known points of the tanh-form GELU, its limits, and the fp16-table
+    form's defining property (every output is an fp16 value; inputs that round to the same fp16 value
+    give the same output)."""
+    x = np.array([0.0, 1.0, -1.0, 3.0, -3.0, 10.0, -10.0], np.float32)
+    g = oracle.gelu_tanh(x)
+    np.testing.assert_allclose(g[:5], [0.0, 0.8411920, -0.1588080, 2.9963627, -0.0036373], rtol=0, atol=2e-7)
+    assert g[5] == 10.0 and abs(g[6]) < 1e-20
+    rng = np.random.default_rng(0)
+    y = rng.normal(0, 2, 4096).astype(np.float32)
+    h = oracle.gelu_tanh(y, through_f16=True)
+    assert np.array_equal(h, h.astype(np.float16).astype(np.float32))
+    assert np.array_equal(h, oracle.gelu_tanh(y.astype(np.float16).astype(np.float32), through_f16=True))
+    np.testing.assert_allclose(h, oracle.gelu_tanh(y), rtol=2e-3, atol=1e-3)

@@ -257,6 +257,75 @@ def test_back_to_back_async_calls_stay_bit_identical(ctx, M, K, N):
     ctx.unload_weights(2)
 
 
+def test_ring_slot_ownership_with_several_items_per_cta(ctx):
+    """More work items than SMs, so every CTA walks several tiles, with builder-group counts, ring depths
+    and slabs per turn that do not divide the rings evenly as asked for: the launcher has to bring them to
+    a combination in which every ring slot keeps one producer and one consumer (an mbarrier parity wait
+    cannot tell use q from use q-2).  With three groups on a four-slot ring this shape used to give wrong
+    sums or run into the bounded wait.  Repeated, because the failure depended on timing."""
+    import torch
+    M, K, N = 2048, 768, 3072
+    c = synth.make_case(M=M, K=K, N=N, v=2, CT=16, seed=77)
+    want = torch.from_numpy(oracle.amm(c.x, c.centroid, c.lut, c.bias, c.scale, 0.0)[0]).cuda()
+    ctx.load_weights(4, c.centroid, c.lut, c.bias, c.scale)
+    x = torch.from_numpy(c.x).cuda()
+    U = P.VARIANT_UMMA
+    for plan in (dict(umma_operand=2, umma_n_tile=192, umma_split=2, umma_groups=3),
+                 dict(umma_operand=2, umma_n_tile=192, umma_split=2, umma_groups=3, umma_sps=1),
+                 dict(umma_operand=2, umma_n_tile=192, umma_split=1, umma_groups=3, umma_stages=5),
+                 dict(umma_operand=2, umma_n_tile=160, umma_split=2, umma_groups=4),
+                 dict(umma_operand=2, umma_n_tile=128, umma_split=16, umma_sps=2),
+                 dict(umma_operand=2, umma_n_tile=128, umma_split=3, umma_groups=3, umma_stages=13),
+                 dict(umma_operand=2, umma_n_tile=64, umma_split=1, umma_groups=3, umma_sps=2),
+                 dict(umma_operand=1, umma_n_tile=128, umma_split=2, umma_groups=3, umma_stages=7),
+                 dict(umma_operand=1, umma_n_tile=256, umma_split=2, umma_groups=3)):
+        ctx.set_plan(4, variant=U, **plan)
+        ys = [torch.empty(M, N, device="cuda") for _ in range(3)]
+        for it in range(12):
+            ctx.amm_host(4, x, ys[it % 3], flags=P.FLAG_ASYNC)
+        ctx.sync()
+        for y in ys:
+            assert torch.equal(y.view(torch.int32), want.view(torch.int32)), plan
+    ctx.unload_weights(4)
+
+
+@pytest.mark.parametrize("M,K,N,v,CT", [(300, 256, 400, 2, 16), (1024, 768, 3072, 2, 16), (200, 96, 48, 3, 12)])
+def test_fused_activation(ctx, M, K, N, v, CT):
+    """GELU applied inside the LUT kernel's epilogue (the reference runs it as a separate pass over the FFN1
+    output, transformer_layer.cpp:503).  The int32 accumulators stay bit-exact; the output is a float
+    function of the bit-exact dequantised value: rel 1e-5 + abs 1e-9 for the fp32 form (hardware exp2 and
+    reciprocal approximations against float64 numpy), at most one fp16 step (rel 2^-10) for the fp16-table form;
+    every plan - direct epilogue, split tiles, tiled output, CUDA-core gather - gives the same bytes;
+    switching the activation off restores the plain output bit for bit."""
+    c = synth.make_case(M=M, K=K, N=N, v=v, CT=CT, seed=11)
+    out, idx, acc = oracle.amm(c.x, c.centroid, c.lut, c.bias, c.scale, 0.0)
+    ctx.load_weights(3, c.centroid, c.lut, c.bias, c.scale)
+    for act, f16 in ((P.ACT_GELU_TANH, False), (P.ACT_GELU_TANH_F16, True)):
+        ctx.set_activation(3, act)
+        want = oracle.gelu_tanh(out, through_f16=f16)
+        first = None
+        for name, plan in variants_for(CT, N, K // v):
+            ctx.set_plan(3, **plan)
+            g_out, g_idx, g_acc = ctx.amm_debug(3, c.x)
+            assert np.array_equal(g_acc, acc), name
+            if f16:
+                np.testing.assert_allclose(g_out, want, rtol=2.0 ** -10, atol=1e-7, err_msg=name)
+                assert np.array_equal(g_out, g_out.astype(np.float16).astype(np.float32)), name
+            else:
+                np.testing.assert_allclose(g_out, want, rtol=1e-5, atol=1e-9, err_msg=name)
+            if first is None:
+                first = g_out
+            assert np.array_equal(g_out.view(np.uint32), first.view(np.uint32)), f"{name}: plans disagree"
+    ctx.set_activation(3, P.ACT_NONE)
+    ctx.set_plan(3, variant=P.VARIANT_AUTO)
+    y = np.zeros_like(out)
+    ctx.amm_host(3, c.x, y)
+    assert np.array_equal(y.view(np.uint32), out.view(np.uint32))
+    with pytest.raises(P.LutAmmError):
+        ctx.set_activation(3, 9)
+    ctx.unload_weights(3)
+
+
 def test_argument_validation(ctx):
     c = synth.make_case(M=4, K=32, N=16, v=2, CT=8, seed=1)
     with pytest.raises(P.LutAmmError) as e:
