@@ -629,10 +629,17 @@ size_t umma_smem_bytes(uint32_t n_tile, uint32_t a_slots, uint32_t b_slots, bool
            kOneHotTabBytes + kNumBarriers * 8 + 16 + 1024;
 }
 constexpr size_t kSmemLimit = 227 * 1024;
+constexpr size_t kSmemOneCtaPerSm = 116 * 1024;  // of 228 KiB per SM
 
 template <uint32_t N_TILE, bool A_TMEM, uint32_t SPS>
 cudaError_t run(const CUtensorMap& map, const UmmaParams& p, uint32_t grid, size_t smem, cudaStream_t s) {
     auto k = lut_onehot_umma_kernel<N_TILE, A_TMEM, SPS>;
+    // Never two of these CTAs on one SM: the second would sit in tcgen05.alloc until the first has
+    // freed its tensor memory, and with split tiles the first may be waiting for the second's slice.
+    // The grid is at most one CTA per SM, but while the preceding kernel still holds some SMs
+    // (programmatic dependent launch) the block scheduler doubles CTAs up wherever two fit - which a
+    // shallow ring with a single builder group does.  More than half an SM's shared memory rules it out.
+    if (smem < kSmemOneCtaPerSm) smem = kSmemOneCtaPerSm;
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     cudaLaunchConfig_t cfg = {};

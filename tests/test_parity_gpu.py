@@ -278,7 +278,10 @@ def test_ring_slot_ownership_with_several_items_per_cta(ctx):
                  dict(umma_operand=2, umma_n_tile=128, umma_split=3, umma_groups=3, umma_stages=13),
                  dict(umma_operand=2, umma_n_tile=64, umma_split=1, umma_groups=3, umma_sps=2),
                  dict(umma_operand=1, umma_n_tile=128, umma_split=2, umma_groups=3, umma_stages=7),
-                 dict(umma_operand=1, umma_n_tile=256, umma_split=2, umma_groups=3)):
+                 dict(umma_operand=1, umma_n_tile=256, umma_split=2, umma_groups=3),
+                 # small enough for two CTAs per SM by registers and ring size: must still get an SM each
+                 dict(umma_operand=2, umma_n_tile=64, umma_split=7, umma_groups=1, umma_stages=2),
+                 dict(umma_operand=2, umma_n_tile=160, umma_split=12, umma_groups=1, umma_stages=4)):
         ctx.set_plan(4, variant=U, **plan)
         ys = [torch.empty(M, N, device="cuda") for _ in range(3)]
         for it in range(12):
