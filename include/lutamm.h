@@ -90,7 +90,11 @@ typedef struct lutamm_lut_params {
 } lutamm_lut_params;
 
 /* GPU execution plan for one layer: what the reference's auto-tuner output
- * (kernel_params in the YAML, src/tuner/auto_tuner.cpp:46-82) becomes on a GPU. */
+ * (kernel_params in the YAML, src/tuner/auto_tuner.cpp:46-82) becomes on a GPU.
+ * The tcgen05 fields are requests: the launcher rounds ring depths down to even numbers, takes the
+ * largest builder-group count not above umma_groups that divides the one-hot ring evenly, and builds one
+ * slab per turn where two would let ring slots change hands - every combination computes the same
+ * result. */
 typedef struct lutamm_plan {
     uint32_t variant;         /* LUTAMM_VARIANT_*                                         */
     uint32_t ccs_tokens;      /* tokens each search thread walks (0 = default)            */
