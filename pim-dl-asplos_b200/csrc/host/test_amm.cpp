@@ -52,6 +52,15 @@ int main(int argc, char** argv) {
     const size_t n_lut = (size_t)lp.num_codebook * lp.num_centroid * lp.output_feature_len;
     const size_t n_out = (size_t)lp.n * lp.output_feature_len;
 
+    // The device first: without one the driver stops here instead of after filling gigabytes of operands.
+    double t1 = W_time();
+    lutamm_ctx* ctx = nullptr;
+    if (lutamm_create(&ctx, (int)prm.gpu_device) != LUTAMM_OK) {
+        std::cerr << "cannot create a GPU context: " << lutamm_last_error(nullptr) << std::endl;
+        return 1;
+    }
+    std::cout << "gpu context create time is " << W_time() - t1 << std::endl;
+
     std::vector<float> input(n_in), centroid(n_cent), bias(lp.output_feature_len), output(n_out);
     std::vector<lut_data_type> lut(n_lut);
     {
@@ -64,14 +73,6 @@ int main(int argc, char** argv) {
         for (auto& v : bias) v = d_c(g_bias);
     }
     std::cout << "data generation finished" << std::endl;
-
-    double t1 = W_time();
-    lutamm_ctx* ctx = nullptr;
-    if (lutamm_create(&ctx, (int)prm.gpu_device) != LUTAMM_OK) {
-        std::cerr << "cannot create a GPU context: " << lutamm_last_error(nullptr) << std::endl;
-        return 1;
-    }
-    std::cout << "gpu context create time is " << W_time() - t1 << std::endl;
 
     // first call uploads the weights (the reference's load_binary + LUT push)
     t1 = W_time();
