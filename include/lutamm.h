@@ -11,8 +11,11 @@
  * Every entry point below names the piece of the reference inference engine it stands
  * in for (paths inside the reference project).  All calls return 0 on success or a
  * negative LUTAMM_E* code; lutamm_last_error() gives the text.  Nothing here aborts
- * the process.  Data pointers may be host or device addresses unless stated; host
- * buffers are staged through pinned memory owned by the context.
+ * the process.  Data pointers may be host or device addresses unless stated.  Host
+ * buffers are copied by cudaMemcpyAsync straight between the caller's memory and device
+ * staging owned by the context: with pinned (page-locked) caller memory the copies overlap
+ * the kernels and each other; pageable memory works but the CUDA runtime serialises such
+ * copies, so the overlap is lost.
  *
  * Layouts (all dense, row-major, the "canonical" forms the reference's weight
  * converter writes): input [M][K] fp32, centroid [CB][CT][v] fp32, LUT [CB][CT][N]
@@ -107,7 +110,8 @@ typedef struct lutamm_plan {
                                  1 = shared memory, 2 = tensor memory (TMEM)             */
     uint32_t umma_sps;        /* tcgen05: 128-byte slabs of the codebook axis a one-hot builder
                                  group takes per turn, 1 or 2 (0 = default; 4 is read as 2)  */
-    uint32_t reserved;
+    uint32_t umma_mma_warps;  /* tcgen05: warps that take turns issuing the MMAs (and lanes that take turns
+                                 issuing the LUT tile copies), 2 or 4 (0 = by tile width)             */
 } lutamm_plan;
 
 /* Device times of the last timed call, milliseconds (CUDA events on the context's stream).
@@ -201,7 +205,9 @@ int lutamm_index_calculation(lutamm_ctx* ctx, int layer_id, const float* input, 
                              uint32_t n_tokens, uint32_t index_format);
 
 /* Replaces pim_lut() (src/host/pim_lut_host.cpp:121-222) with prepare_input_index()
- * (:40-118) folded into the kernel's address arithmetic: index is uint8 [n_tokens][CB]. */
+ * (:40-118) folded into the kernel's address arithmetic: index is uint8 [n_tokens][CB].
+ * An index >= num_centroid selects no table row: that codebook contributes 0 to every
+ * accumulator of the token (both kernel variants), and nothing outside the table is read. */
 int lutamm_pim_lut(lutamm_ctx* ctx, int layer_id, const uint8_t* index, float* output,
                    uint32_t n_tokens, uint32_t flags);
 

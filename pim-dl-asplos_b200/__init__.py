@@ -65,11 +65,11 @@ class Plan(ctypes.Structure):
     _fields_ = [("variant", ctypes.c_uint32), ("ccs_tokens", ctypes.c_uint32), ("gather_cfg", ctypes.c_uint32),
                 ("umma_n_tile", ctypes.c_uint32), ("umma_split", ctypes.c_uint32), ("umma_stages", ctypes.c_uint32),
                 ("umma_groups", ctypes.c_uint32), ("umma_operand", ctypes.c_uint32),
-                ("umma_sps", ctypes.c_uint32), ("reserved", ctypes.c_uint32)]
+                ("umma_sps", ctypes.c_uint32), ("umma_mma_warps", ctypes.c_uint32)]
 
     def as_dict(self):
         return {k: getattr(self, k) for k in ("variant", "ccs_tokens", "gather_cfg", "umma_n_tile", "umma_split",
-                                              "umma_stages", "umma_groups", "umma_operand", "umma_sps")}
+                                              "umma_stages", "umma_groups", "umma_operand", "umma_sps", "umma_mma_warps")}
 
 
 class Timings(ctypes.Structure):

@@ -1,5 +1,6 @@
 #include "amm_host.h"
 
+#include <cstring>
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -16,8 +17,27 @@ struct Key {
     }
 };
 
+// What the resident copy was loaded with: a later call that names the same three buffers but other
+// parameter blocks (scale, LUT bias, shape, tile sizes, table layout) must not be served by it.
+struct Resident {
+    int id;
+    IndexCalcParams ip;
+    LUTParams lp;
+    uint32_t lut_layout;
+};
+
+// Everything except `n` (the token count of the call, which the kernels take per call) and the
+// host-thread counts decides what is resident or how the output is addressed.
+bool same_params(const Resident& r, const IndexCalcParams& ip, const LUTParams& lp, uint32_t lut_layout) {
+    IndexCalcParams a = r.ip, b = ip;
+    LUTParams c = r.lp, d = lp;
+    a.n = b.n = 0; a.num_threads = b.num_threads = 0;
+    c.n = d.n = 0; c.num_threads = d.num_threads = 0;
+    return r.lut_layout == lut_layout && std::memcmp(&a, &b, sizeof a) == 0 && std::memcmp(&c, &d, sizeof c) == 0;
+}
+
 std::mutex g_mu;
-std::map<Key, int> g_layers;           // weights already resident -> layer id
+std::map<Key, Resident> g_layers;      // weights already resident -> layer id and what it was loaded with
 std::map<lutamm_ctx*, int> g_next_id;  // ids handed out by amm_host() start high, away from user ids
 constexpr int kFirstAutoId = 1 << 20;
 
@@ -50,6 +70,12 @@ int amm_host_impl(lutamm_ctx* ctx, float* input_tensor, float* centroid_tensor, 
         std::lock_guard<std::mutex> lk(g_mu);
         const Key k{ctx, centroid_tensor, lut_table, bias_tensor};
         auto it = g_layers.find(k);
+        if (it != g_layers.end() && !same_params(it->second, index_params, lut_params, lut_layout)) {
+            // same buffers, different operator: the resident copy is stale
+            lutamm_unload_weights(ctx, it->second.id);
+            g_layers.erase(it);
+            it = g_layers.end();
+        }
         if (it == g_layers.end()) {
             int& next = g_next_id[ctx];
             if (next < kFirstAutoId) next = kFirstAutoId;
@@ -58,9 +84,9 @@ int amm_host_impl(lutamm_ctx* ctx, float* input_tensor, float* centroid_tensor, 
                                                       reinterpret_cast<const lutamm_index_params*>(&index_params),
                                                       reinterpret_cast<const lutamm_lut_params*>(&lut_params), lut_layout);
             if (rc != LUTAMM_OK) return rc;
-            g_layers.emplace(k, id);
+            g_layers.emplace(k, Resident{id, index_params, lut_params, lut_layout});
         } else {
-            id = it->second;
+            id = it->second.id;
         }
     }
     return lutamm_amm(ctx, id, input_tensor, output_tensor, index_params.n, flags);
@@ -79,7 +105,7 @@ void amm_host_forget(lutamm_ctx* ctx) {
     std::lock_guard<std::mutex> lk(g_mu);
     for (auto it = g_layers.begin(); it != g_layers.end();) {
         if (it->first.ctx == ctx) {
-            lutamm_unload_weights(ctx, it->second);
+            lutamm_unload_weights(ctx, it->second.id);
             it = g_layers.erase(it);
         } else {
             ++it;

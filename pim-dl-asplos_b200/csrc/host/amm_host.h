@@ -6,8 +6,11 @@
 //
 // The reference pushes the whole LUT to the DPUs on every call (pim_lut_host.cpp:143).
 // Here the weights named by (centroid, lut, bias) are uploaded the first time they are seen
-// and stay resident; later calls with the same pointers only run the kernels.  Pointers may
-// be host or device addresses.  Returns 0 or a negative LUTAMM_E* code (the reference
+// and stay resident; later calls with the same three pointers AND the same parameter blocks
+// (everything but n and the host-thread counts) only run the kernels, a call with the same
+// pointers but other parameters reloads.  The association is by address, not by content: a
+// caller that refills the same buffers with other weights calls amm_host_forget() first.
+// Pointers may be host or device addresses.  Returns 0 or a negative LUTAMM_E* code (the reference
 // returns void and aborts on error).
 #pragma once
 #include "defines.h"

@@ -157,12 +157,17 @@ lut_gather_kernel(const __grid_constant__ CUtensorMap lut_map, LutArgs a, uint32
             const unsigned char* row0 = base + (size_t)c * a.CT * N_TILE;
 #pragma unroll
             for (int t = 0; t < TOK; ++t) {
-                const uint32_t i = my_idx[t * cb_blk + c];
+                // An index may come from a caller (lutamm_pim_lut): one that is out of range for the
+                // codebook reads the last row, inside the stage, and contributes nothing - the same as
+                // the tcgen05 kernel, whose one-hot row is all zero for such an index.
+                const uint32_t i_raw = my_idx[t * cb_blk + c];
+                const uint32_t i = min(i_raw, a.CT - 1u);
+                const uint32_t keep = i_raw < a.CT ? 0xFFFFFFFFu : 0u;
                 LutWord<COLS> w;
                 w.load(row0 + i * N_TILE);
 #pragma unroll
                 for (int k = 0; k < COLS; ++k)
-                    acc[t][k] = __dp4a((int)w.w[k >> 2], (int)(1u << (8 * (k & 3))), acc[t][k]);
+                    acc[t][k] = __dp4a((int)(w.w[k >> 2] & keep), (int)(1u << (8 * (k & 3))), acc[t][k]);
             }
         }
         __syncwarp();

@@ -209,13 +209,23 @@ int run_lut(lutamm_ctx* c, Layer& L, const uint8_t* d_idx, float* d_out, int32_t
         up.stages = plan.umma_stages;
         up.groups = plan.umma_groups;
         if (plan.umma_sps) up.sps = plan.umma_sps;
+        up.mma_warps = plan.umma_mma_warps;
         if (!umma_tile_ok(up.n_tile, a_tmem))
             return fail(c, LUTAMM_EINVAL, "umma_n_tile must be 64, 128 or 256 with the one-hot operand in shared memory, "
                                           "64, 128, 160 or 192 with it in tensor memory");
         if (!L.d_lut_t) {
+            // First tcgen05 call for this layer: make the K-major copy of the table.  The kernel that
+            // follows is a programmatic dependent launch whose TMA producer does not wait for the
+            // preceding grid, so the copy has to be complete - not merely queued - before it starts.
             const size_t bytes = (size_t)L.CB * L.CT * L.N;
             CU_TRY(c, cudaMalloc(&L.d_lut_t, bytes));
-            CU_TRY(c, launch_transpose_lut(L.d_lut, L.d_lut_t, L.CB * L.CT, L.N, c->stream));
+            cudaError_t te = launch_transpose_lut(L.d_lut, L.d_lut_t, L.CB * L.CT, L.N, c->stream);
+            if (te == cudaSuccess) te = cudaStreamSynchronize(c->stream);
+            if (te != cudaSuccess) {
+                cudaFree(L.d_lut_t);
+                L.d_lut_t = nullptr;
+                return fail(c, LUTAMM_ECUDA, std::string("LUT transpose: ") + cudaGetErrorString(te));
+            }
             ++c->launches;
         }
         const int slot = umma_tile_slot(up.n_tile);
@@ -685,6 +695,8 @@ int lutamm_set_plan(lutamm_ctx* c, int layer_id, const lutamm_plan* plan) {
                                       "0, 64, 128, 160 or 192 with it in tensor memory");
     if (plan->umma_sps != 0 && plan->umma_sps != 1 && plan->umma_sps != 2 && plan->umma_sps != 4)
         return fail(c, LUTAMM_EINVAL, "umma_sps must be 0, 1, 2 or 4");
+    if (plan->umma_mma_warps != 0 && plan->umma_mma_warps != 2 && plan->umma_mma_warps != 4)
+        return fail(c, LUTAMM_EINVAL, "umma_mma_warps must be 0, 2 or 4");
     if (plan->variant == LUTAMM_VARIANT_UMMA && !umma_supported(L->CB, L->CT, L->N))
         return fail(c, LUTAMM_EUNSUPPORTED, "tcgen05 variant does not cover this shape");
     L->plan = *plan;

@@ -75,6 +75,8 @@ extern "C" int lutamm_amm_static_scratch(int device, void* cuda_stream, const fl
     const uint32_t M = ip->n, K = ip->input_feature_len, CB = ip->num_codebook, CT = ip->num_centroid;
     const uint32_t N = lp->output_feature_len;
     if (!K || !CB || !CT || !N || K % CB) return fail(LUTAMM_EINVAL, "bad shape: need input_feature_len % num_codebook == 0 and positive sizes");
+    if (ip->sub_vec_len && ip->sub_vec_len != K / CB)
+        return fail(LUTAMM_EINVAL, "sub_vec_len != input_feature_len / num_codebook");
     if (lp->num_codebook != CB || lp->num_centroid != CT || lp->n != M)
         return fail(LUTAMM_EINVAL, "index and LUT parameter blocks disagree");
     if (CT > 256) return fail(LUTAMM_EINVAL, "num_centroid > 256 does not fit the uint8 index");
@@ -142,11 +144,13 @@ extern "C" int lutamm_amm_static_scratch(int device, void* cuda_stream, const fl
     e = launch_gather(la, map, cfg, d_err, s, &why);
     if (e != cudaSuccess) return fail(LUTAMM_ECUDA, why ? why : (std::string("gather launch: ") + cudaGetErrorString(e)));
 
+    // The error word comes back on the caller's stream, behind the kernels; the legacy default stream
+    // (which would serialise against every blocking stream of the process) is not touched.
+    uint32_t h_err = 0;
+    e = cudaMemcpyAsync(&h_err, d_err, sizeof h_err, cudaMemcpyDeviceToHost, s);
+    if (e != cudaSuccess) return fail(LUTAMM_ECUDA, std::string("cudaMemcpyAsync(error word): ") + cudaGetErrorString(e));
     e = cudaStreamSynchronize(s);
     if (e != cudaSuccess) return fail(LUTAMM_ECUDA, std::string("cudaStreamSynchronize: ") + cudaGetErrorString(e));
-    uint32_t h_err = 0;
-    e = cudaMemcpy(&h_err, d_err, sizeof h_err, cudaMemcpyDeviceToHost);
-    if (e != cudaSuccess) return fail(LUTAMM_ECUDA, std::string("cudaMemcpy(error word): ") + cudaGetErrorString(e));
     if (h_err) return fail(LUTAMM_EDEVICE, "a kernel gave up on a bounded wait; output is not valid");
     return LUTAMM_OK;
 }

@@ -5,8 +5,9 @@ instead of the context's grow-only arena.
 
 Called through the C ABI, twice in a row with different shapes so the second call meets the
 first call's leftovers in the shared array, and compared with the regular lutamm_amm() entry
-point: same kernels, same arithmetic, so the fp32 outputs must be bit-identical (the suite's
-bar for this path; 1e-5 relative is the stated tolerance).  This file sorts last on purpose:
+point (same kernels, same arithmetic, so the fp32 outputs must be bit-identical) and with the
+CPU oracle (bit-identical too: the suite's bar for this path; 1e-5 relative is the stated
+tolerance).  This file sorts last on purpose:
 a run that stops at the first failure has then already run every other test.
 """
 import ctypes
@@ -14,6 +15,7 @@ import ctypes
 import numpy as np
 import pytest
 
+import oracle
 import pim_dl_asplos_b200 as P
 from pim_dl_asplos_b200 import synth
 
@@ -43,6 +45,9 @@ def _run_both(lib, ctx, M, K, N, v, CT, seed, layer_id):
     a, b = y_static.cpu().numpy(), y_ctx.cpu().numpy()
     np.testing.assert_allclose(a, b, rtol=1e-5, atol=0)
     assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+    want = oracle.amm(c.x, c.centroid, c.lut, c.bias, c.scale, c.lut_bias)[0]
+    np.testing.assert_allclose(a, want, rtol=1e-5, atol=0)
+    assert np.array_equal(a.view(np.uint32), want.view(np.uint32)), "static-scratch output differs from the CPU oracle"
 
 
 def test_static_scratch_entry_point_matches_the_regular_one_twice():
@@ -70,3 +75,8 @@ def test_static_scratch_rejects_what_does_not_fit():
     rc = lib.lutamm_amm_static_scratch(0, None, host.ctypes.data, t.data_ptr(), t.data_ptr(), t.data_ptr(), t.data_ptr(),
                                        ctypes.byref(ip), ctypes.byref(lp))
     assert rc == P.EINVAL and b"device memory" in lib.lutamm_static_scratch_last_error()
+    ip, lp = P.make_params(4, 32, 16, 16, 8, 0.01, 0.0)
+    ip.sub_vec_len = 3                                                   # K / CB is 2
+    rc = lib.lutamm_amm_static_scratch(0, None, t.data_ptr(), t.data_ptr(), t.data_ptr(), t.data_ptr(), t.data_ptr(),
+                                       ctypes.byref(ip), ctypes.byref(lp))
+    assert rc == P.EINVAL and b"sub_vec_len" in lib.lutamm_static_scratch_last_error()
