@@ -16,8 +16,20 @@ prints ONE JSON line.  Three measurements go into it:
             bytes per step divided by its device time, taken live with CUDA-event pairs
             around each launch, against the measured HBM copy bandwidth
 
-and, at one GPU, `cpu_baseline`: the CPU oracle timed on this machine's host cores on a
+and, at one GPU, `cpu_baseline`: the reference's CPU AMM timed on this machine's host cores on a
 bounded sample.  `--impl reference` prints the CPU path's own line for the same workload.
+
+Further keys of the line:
+  parity_ok   every rank compared a row subsample of what the timed calls wrote with the CPU oracle
+              (bit for bit); false on any rank makes it false
+  int8_peak   the GPU's int8 tensor rate measured in the same process (lutamm_measure_int8_peak): the
+              denominator of roofline.tensor_view
+  c1          (one GPU) the single BERT-base FFN1 linear at 512 tokens: step and kernel times over 200
+              event-timed repetitions and their HBM-roofline fractions
+  sustained   (one GPU) the device-resident step looped back to back for two seconds, with the SM clock
+              sampled meanwhile
+  c5_sharded  one large AMM (65536 tokens, 4096 -> 16384) split over the ranks, strong scaling, both ways:
+              by tokens (no collective) and by output columns (NCCL all-gather inside the library call)
 
 Multi-GPU (launched by torchrun, one rank per GPU): tokens are sharded across ranks and the
 weights replicated, so there is no data-path collective (weak scaling: every rank runs the
@@ -59,6 +71,8 @@ def parse_args():
     ap.add_argument("--ct", type=int, default=None, help="override centroid count (c5 sweep)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="skip the c1 / sustained / c5_sharded legs")
+    ap.add_argument("--c5-tokens", type=int, default=65536, help="tokens of the c5_sharded leg (all ranks together)")
     return ap.parse_args()
 
 
@@ -74,7 +88,7 @@ def measured_bf16_tflops():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
         return float(json.load(open(p)).get("bf16_tflops", 0.0)) or None
-    return 1590.0  # the pool's earlier measurement, used when the file is absent
+    return 1590.0  # a typical B200 figure, used when the file is absent
 
 
 def recorded_traffic(workload: str):
@@ -256,6 +270,8 @@ def run_ours(args):
     ctx = P.LutAmmContext(local)
     stream = torch.cuda.Stream()
     ctx.set_stream(stream.cuda_stream)
+    if world > 1:
+        ctx.shard_init()   # the library's own NCCL communicator, for the sharded entry points
 
     layers = []
     for li, (name, K, N) in enumerate(w["linears"]):
@@ -282,19 +298,19 @@ def run_ours(args):
             L["x_dev"] = torch.from_numpy(L["x_host"]).cuda(non_blocking=False)
             L["y_dev"] = torch.empty(M, L["n_loc"], device="cuda", dtype=torch.float32)
             if args.shard == "n" and world > 1:
-                L["y_all"] = torch.empty(world * M, L["n_loc"], device="cuda", dtype=torch.float32)
-                L["y_full"] = torch.empty(M, L["N"], device="cuda", dtype=torch.float32)
+                L["y_all"] = torch.empty(world, M, L["n_loc"], device="cuda", dtype=torch.float32)
         flush = torch.empty(256 * 1024 * 1024, device="cuda", dtype=torch.uint8)
     stream.synchronize()
 
     def step_device():
         for li, L in enumerate(layers):
-            ctx.amm_host(li, L["x_dev"], L["y_dev"], n_tokens=M, flags=P.FLAG_ASYNC)
             if args.shard == "n" and world > 1:
-                with torch.cuda.stream(stream):
-                    dist.all_gather_into_tensor(L["y_all"], L["y_dev"])
-                    # interleave the column slabs into row-major [M][N]
-                    L["y_full"].view(M, world, L["n_loc"]).copy_(L["y_all"].view(world, M, L["n_loc"]).permute(1, 0, 2))
+                # this rank's column slab into block `rank` of [world][M][N/world], one in-place all-gather
+                # inside the library call; the buffer is the reference's tiled output for lut_parallelism = world
+                ctx.amm_column_sharded(li, L["x_dev"], L["y_all"], n_tokens=M, search_mode=P.SHARD_SEARCH_SPLIT,
+                                       flags=P.FLAG_ASYNC)
+            else:
+                ctx.amm_host(li, L["x_dev"], L["y_dev"], n_tokens=M, flags=P.FLAG_ASYNC)
 
     def barrier():
         if world > 1:
@@ -359,14 +375,77 @@ def run_ours(args):
                 "search_kernel_ms_per_step": ccs_ms,
                 "search_algorithmic_bytes_per_step": sum(a["ccs"] for a in alg),
                 "whole_step_frac": (sum(a["total"] for a in alg) / (ms_per_step * 1e-3) / 1e9) / peak}
+    # the search kernel against both of its roofs: HBM, and fp32 issue (one lane-instruction per clock per
+    # lane: 128 lanes x SMs x clock; the unfused reference arithmetic costs about 3.5 x CT lane-instructions
+    # per activation float at v = 2 with packed adds and multiplies, 7 per centroid per sub-vector)
+    ccs_bytes = sum(a["ccs"] for a in alg)
+    roofline["search_frac_hbm"] = (ccs_bytes / (ccs_ms * 1e-3) / 1e9) / peak if ccs_ms > 0 else None
+    lane_instr = sum(M * (L["K"] // v) * CT * (3.5 * v) for L in layers)
+    sm_clock = 1.965e9
+    roofline["search_issue_bound"] = {"lane_instructions": lane_instr,
+                                      "frac_of_fp32_issue": lane_instr / (ccs_ms * 1e-3) / (148 * 128 * sm_clock) if ccs_ms > 0 else None,
+                                      "assumes": "3.5 x num_centroid lane-instructions per activation float, 148 SMs x 128 lanes at 1965 MHz"}
     # the same launches seen as what they are on the default plan, an int8 one-hot contraction on the
     # tensor pipe: 2*M*N*CB*CT operations; against twice the measured dense bf16 rate (the int8 rate is
     # not in MEASURED_PEAKS.json; nominally it is twice bf16's)
     ops = sum(2.0 * M * L["n_loc"] * (L["K"] // v) * CT for L in layers)
     bf16 = measured_bf16_tflops()
     roofline["tensor_view"] = {"int8_tops": ops / (lut_ms * 1e-3) / 1e12,
-                               "assumed_int8_peak_tops": 2.0 * bf16 if bf16 else None,
-                               "frac": (ops / (lut_ms * 1e-3) / 1e12) / (2.0 * bf16) if bf16 else None}
+                               "twice_measured_bf16_tops": 2.0 * bf16 if bf16 else None,
+                               "frac": (ops / (lut_ms * 1e-3) / 1e12) / (2.0 * bf16) if bf16 else None,
+                               "frac_of": "twice the measured dense bf16 rate"}
+
+    # ---- parity of what the timed calls wrote: a row subsample of every linear against the CPU oracle
+    if rank == 0:
+        import oracle
+        oracle.build()
+    barrier()
+    import oracle
+
+    def rows_ok(got_rows, x_rows, K, N, v_, CT_, stream_id, n_lo=0, n_hi=None):
+        cen, lut, bias = synth.make_weights(K, N, v_, CT_, seed=0, stream=stream_id)
+        want = oracle.amm(np.ascontiguousarray(x_rows), cen, lut, bias, 0.01, 0.0)[0][:, n_lo:n_hi]
+        return bool(np.array_equal(np.ascontiguousarray(got_rows).view(np.uint32), np.ascontiguousarray(want).view(np.uint32)))
+
+    step_device()
+    ctx.sync()
+    parity_ok = True
+    for li, L in enumerate(layers):
+        rows = np.unique(np.concatenate([np.arange(0, M, max(1, M // 16)), [M - 1]]))
+        if args.shard == "n" and world > 1:
+            got = L["y_all"][:, rows, :].permute(1, 0, 2).reshape(len(rows), L["N"]).cpu().numpy()
+            if L["N"] % (16 * world) == 0:   # equal slabs: the blocks in rank order are the columns in order
+                parity_ok &= rows_ok(got, L["x_host"][rows], L["K"], L["N"], v, CT, li)
+        else:
+            got = L["y_dev"][torch.from_numpy(rows).cuda()].cpu().numpy()
+            parity_ok &= rows_ok(got, L["x_host"][rows], L["K"], L["N"], v, CT, li)
+    if world > 1:
+        t_ok = torch.tensor([1 if parity_ok else 0], device="cuda")
+        dist.all_reduce(t_ok, op=dist.ReduceOp.MIN)
+        parity_ok = bool(t_ok.item())
+
+    # ---- the int8 tensor rate of this GPU, measured here: the tensor-side denominator
+    int8_peak = None
+    if rank == 0:
+        pk = ctx.measure_int8_peak()
+        int8_peak = {"tops": pk["tops"], "mac_per_clk_per_sm": pk["mac_per_clk_sm"], "sm_mhz_during": pk["sm_mhz"],
+                     "how": "lutamm_measure_int8_peak: tcgen05.mma kind::i8 128x256x32 back to back on every SM, both "
+                            "operands on chip, four issuing warps per CTA; best of 3 after a warm-up; TOPS by CUDA events, "
+                            "MAC/clk/SM by a CTA's own cycle counter"}
+        tv = roofline["tensor_view"]
+        tv["measured_int8_peak_tops"] = pk["tops"]
+        tv["frac"] = tv["int8_tops"] / pk["tops"] if pk["tops"] else None
+        tv["frac_of"] = "measured int8 rate (int8_peak)"
+
+    extras = {}
+    if not args.no_extras:
+        if rank == 0 and world == 1 and args.workload != "c1":
+            extras["c1"] = leg_c1(ctx, stream, flush, peak, P, synth, torch)
+        if rank == 0 and world == 1 and args.shard == "m":
+            extras["sustained"] = leg_sustained(step_device, ctx, stream, M, local, torch)
+        if args.workload == "c2" and args.shard == "m":
+            barrier()
+            extras["c5_sharded"] = leg_c5_sharded(ctx, stream, args.c5_tokens, rank, world, P, synth, torch, dist, oracle, barrier)
 
     # ---- end to end: pinned host buffers through the public call, copies inside the timing
     e2e = None
@@ -420,8 +499,8 @@ def run_ours(args):
                 torch.cuda.synchronize()
                 best = max(best, reps * nbytes / (e0.elapsed_time(e1) * 1e-3) / 1e9)
             rates.append(best)
-        # both directions at once (two streams): on some hosts of this pool the two directions add up
-        # to little more than one (the link behaves half duplex), on others to almost twice
+        # both directions at once (two streams): on some hosts the two directions add up to little
+        # more than one (the link behaves half duplex), on others to almost twice
         s_a, s_b = torch.cuda.Stream(), torch.cuda.Stream()
         duplex = 0.0
         for _ in range(3):
@@ -488,11 +567,190 @@ def run_ours(args):
                 "scaling": "weak", "vs_baseline": None, "dtype": "fp32 search / int8->int32 gather", "data": "synthetic",
                 "config": config_dict(args, w), "plans": [L["plan"] for L in layers],
                 "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": gpu_launches, "clocks": clocks,
-                "graph_replay": graph_replay}
+                "graph_replay": graph_replay, "parity_ok": parity_ok, "int8_peak": int8_peak}
+        line.update(extras)
         print(json.dumps(line), flush=True)
+    if world > 1:
+        ctx.shard_finalize()
     ctx.close()
     if world > 1:
         dist.destroy_process_group()
+
+
+# --------------------------------------------------------------------------- extra legs of our arm
+def leg_c1(ctx, stream, flush, peak, P, synth, torch):
+    """The shape the HBM-roofline target is quoted on: one BERT-base FFN1 linear, 512 tokens, 768 -> 3072, v = 2,
+    16 centroids.  200 repetitions, each timed by its own CUDA-event pair with the L2 evicted before it."""
+    w = synth.WORKLOADS["c1"]
+    M, (_, K, N), v, CT = w["M"], w["linears"][0], w["v"], w["CT"]
+    cen, lut, bias = synth.make_weights(K, N, v, CT, seed=0)
+    lid = 900
+    ctx.load_weights(lid, cen, lut, bias, 0.01, 0.0)
+    with torch.cuda.stream(stream):
+        x = torch.from_numpy(synth.make_input(M, K, seed=0)).cuda()
+        y = torch.empty(M, N, device="cuda", dtype=torch.float32)
+    for _ in range(5):
+        ctx.amm_host(lid, x, y, n_tokens=M, flags=P.FLAG_ASYNC)
+    ctx.sync()
+    reps = 200
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(reps)]
+    with torch.cuda.stream(stream):
+        for s0, e0 in ev:
+            flush.zero_()
+            s0.record(stream)
+            ctx.amm_host(lid, x, y, n_tokens=M, flags=P.FLAG_ASYNC)
+            e0.record(stream)
+    ctx.sync()
+    step_ms = sorted(s0.elapsed_time(e0) for s0, e0 in ev)
+    ctx.enable_timing(True)
+    lut_t, ccs_t = [], []
+    for _ in range(reps):
+        with torch.cuda.stream(stream):
+            flush.zero_()
+        ctx.amm_host(lid, x, y, n_tokens=M)
+        t = ctx.timings()
+        lut_t.append(t["lut_kernel_ms"])
+        ccs_t.append(t["index_calc_ms"])
+    ctx.enable_timing(False)
+    # warm: the same call back to back without eviction (LUT and activations stay in the 126 MB L2)
+    with torch.cuda.stream(stream):
+        s0, e0 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record(stream)
+        for _ in range(reps):
+            ctx.amm_host(lid, x, y, n_tokens=M, flags=P.FLAG_ASYNC)
+        e0.record(stream)
+    ctx.sync()
+    warm_ms = s0.elapsed_time(e0) / reps
+    ctx.unload_weights(lid)
+    b = synth.algorithmic_bytes(M, K, N, v, CT)
+    med = lambda a: float(statistics.median(a))
+    lut_ms, ccs_ms, ms = med(lut_t), med(ccs_t), med(step_ms)
+    return {"workload": w["what"], "reps": reps, "ms_per_step": ms, "ms_per_step_min": step_ms[0], "tokens_per_s": M / (ms * 1e-3),
+            "lut_kernel_ms": lut_ms, "search_kernel_ms": ccs_ms,
+            "lut_kernel_frac_hbm": b["lut"] / (lut_ms * 1e-3) / 1e9 / peak,
+            "search_kernel_frac_hbm": b["ccs"] / (ccs_ms * 1e-3) / 1e9 / peak,
+            "whole_op_frac_hbm": b["total"] / (ms * 1e-3) / 1e9 / peak,
+            "ms_per_step_l2_warm": warm_ms, "whole_op_frac_hbm_l2_warm": b["total"] / (warm_ms * 1e-3) / 1e9 / peak,
+            "algorithmic_bytes": b, "l2_flush_between_steps": True, "timing": "median of per-repetition CUDA-event pairs"}
+
+
+def leg_sustained(step_device, ctx, stream, M, device, torch):
+    """The device-resident step looped back to back for two seconds, clocks sampled meanwhile: long enough
+    for a power-capped clock, and for a utilisation sampler, to see it.  No eviction between steps here."""
+    for _ in range(20):
+        step_device()
+    ctx.sync()
+    sampler = ClockSampler(device)
+    sampler.start()
+    time.sleep(0.3)
+    chunk, steps, total_ms = 500, 0, 0.0
+    t_end = time.perf_counter() + 2.0
+    while time.perf_counter() < t_end or steps == 0:
+        s0, e0 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            s0.record(stream)
+            for _ in range(chunk):
+                step_device()
+            e0.record(stream)
+        ctx.sync()
+        total_ms += s0.elapsed_time(e0)
+        steps += chunk
+    clocks = sampler.stop()
+    ms = total_ms / steps
+    mhz = clocks.get("sm_mhz")
+    return {"seconds": total_ms * 1e-3, "steps": steps, "ms_per_step": ms, "tokens_per_s": M / (ms * 1e-3), "clocks": clocks,
+            "ms_times_mhz": ms * mhz if mhz else None, "l2_flush_between_steps": False}
+
+
+def leg_c5_sharded(ctx, stream, m_total, rank, world, P, synth, torch, dist, oracle, barrier):
+    """One large AMM split over the ranks (strong scaling): m_total tokens, 4096 -> 16384, v = 2, 16 centroids.
+    (m) tokens: m_total / G rows per rank, weights replicated, no collective.  (n) output columns: all rows, N / G
+    columns per rank, the slabs all-gathered in place by the library (lutamm_amm_column_sharded) - once with every
+    rank searching all tokens, once with the search split and the uint8 indices all-gathered.  Inputs are seeded
+    tensors generated on the GPU (a gigabyte of activations per rank); device times, max over ranks."""
+    K, N, v, CT = 4096, 16384, 2, 16
+    CB = K // v
+    if m_total % (128 * world) or N % (16 * world):
+        return {"skipped": "token or column count does not split evenly over the ranks"}
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(1234)
+    with torch.cuda.stream(stream):
+        x = torch.randn(m_total, K, device="cuda", generator=gen)                       # the same on every rank
+        cen = torch.randn(CB, CT, v, device="cuda", generator=gen)
+        lut = torch.randint(-127, 128, (CB, CT, N), device="cuda", generator=gen, dtype=torch.int8)
+        bias = torch.randn(N, device="cuda", generator=gen) * 0.02
+    stream.synchronize()
+    m_loc, n_loc = m_total // world, N // world
+    rows = np.unique(np.concatenate([np.arange(0, m_total, m_total // 8), [m_total - 1]]))
+    want = oracle.amm(x[torch.from_numpy(rows).cuda()].cpu().numpy(), cen.cpu().numpy(), lut.cpu().numpy(), bias.cpu().numpy(), 0.01, 0.0)[0]
+
+    def timed(fn, reps=3):
+        fn()
+        ctx.sync()
+        barrier()
+        s0, e0 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            s0.record(stream)
+            for _ in range(reps):
+                fn()
+            e0.record(stream)
+        ctx.sync()
+        t = torch.tensor([s0.elapsed_time(e0) / reps], device="cuda", dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def all_ok(ok):
+        t = torch.tensor([1 if ok else 0], device="cuda")
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        return bool(t.item())
+
+    out = {"tokens": m_total, "K": K, "N": N, "sub_vec_len": v, "num_centroid": CT, "scaling": "strong", "world": world}
+    # ---- (m) tokens
+    ctx.load_weights(910, cen, lut, bias, 0.01, 0.0)
+    y_m = torch.empty(m_loc, N, device="cuda", dtype=torch.float32)
+    x_m = x[rank * m_loc:(rank + 1) * m_loc]
+    ms = timed(lambda: ctx.amm_token_sharded(910, x_m, y_m, m_total, gather=False, flags=P.FLAG_ASYNC))
+    mine = [(i, r - rank * m_loc) for i, r in enumerate(rows) if rank * m_loc <= r < (rank + 1) * m_loc]
+    ok = all(np.array_equal(y_m[j].cpu().numpy().view(np.uint32), want[i].view(np.uint32)) for i, j in mine)
+    out["m"] = {"ms": ms, "tokens_per_s": m_total / (ms * 1e-3), "collective_ms": 0.0, "relayout_ms": 0.0, "parity_ok": all_ok(ok),
+                "what": "tokens split, weights replicated, output stays sharded"}
+    del y_m
+    ctx.unload_weights(910)
+    # ---- (n) output columns
+    ctx.load_weights(911, cen, lut[:, :, rank * n_loc:(rank + 1) * n_loc].contiguous(), bias[rank * n_loc:(rank + 1) * n_loc].contiguous(), 0.01, 0.0)
+    del lut
+    y_all = torch.empty(world, m_total, n_loc, device="cuda", dtype=torch.float32)
+    res = {}
+    for name, mode in (("search_replicated", P.SHARD_SEARCH_REPLICATED), ("search_split", P.SHARD_SEARCH_SPLIT)):
+        res[name] = timed(lambda: ctx.amm_column_sharded(911, x, y_all, n_tokens=m_total, search_mode=mode, flags=P.FLAG_ASYNC))
+    got = y_all[:, torch.from_numpy(rows).cuda(), :].permute(1, 0, 2).reshape(len(rows), N).cpu().numpy()
+    ok = bool(np.array_equal(got.view(np.uint32), want.view(np.uint32)))
+    # the parts: this rank's kernels alone (world-size-1 call on its slab), the all-gather alone, and the optional
+    # re-layout to row-major [M][N] for callers that do not take the reference's slab-major layout
+    kern = timed(lambda: ctx.amm_host(911, x, y_all[rank], n_tokens=m_total, flags=P.FLAG_ASYNC))
+    coll = 0.0
+    if world > 1:
+        def gather_only():
+            with torch.cuda.stream(stream):
+                dist.all_gather_into_tensor(y_all.view(world * m_total, n_loc), y_all[rank])
+        coll = timed(gather_only)
+    y_full = torch.empty(m_total, N, device="cuda", dtype=torch.float32)
+
+    def relayout():
+        with torch.cuda.stream(stream):
+            y_full.view(m_total, world, n_loc).copy_(y_all.permute(1, 0, 2))
+    rel = timed(relayout)
+    best = min(res.values())
+    gathered_bytes = (world - 1) * m_total * n_loc * 4      # received per rank
+    out["n"] = {"ms": best, "tokens_per_s": m_total / (best * 1e-3), "ms_by_search_mode": res, "kernels_ms": kern, "collective_ms": coll,
+                "relayout_ms": rel, "tokens_per_s_with_relayout": m_total / ((best + rel) * 1e-3),
+                "allgather_gbs_per_rank": gathered_bytes / (coll * 1e-3) / 1e9 if coll else None, "parity_ok": all_ok(ok),
+                "what": "columns split, all tokens on every rank, slabs all-gathered in place into [G][M][N/G] "
+                        "(the reference's tiled output for lut_parallelism = G); relayout = optional copy to row-major"}
+    ctx.unload_weights(911)
+    return out
 
 
 def main():

@@ -110,8 +110,7 @@ typedef struct lutamm_plan {
                                  1 = shared memory, 2 = tensor memory (TMEM)             */
     uint32_t umma_sps;        /* tcgen05: 128-byte slabs of the codebook axis a one-hot builder
                                  group takes per turn, 1 or 2 (0 = default; 4 is read as 2)  */
-    uint32_t umma_mma_warps;  /* tcgen05: warps that take turns issuing the MMAs (and lanes that take turns
-                                 issuing the LUT tile copies), 2 or 4 (0 = by tile width)             */
+    uint32_t reserved;
 } lutamm_plan;
 
 /* Device times of the last timed call, milliseconds (CUDA events on the context's stream).
@@ -211,6 +210,45 @@ int lutamm_index_calculation(lutamm_ctx* ctx, int layer_id, const float* input, 
 int lutamm_pim_lut(lutamm_ctx* ctx, int layer_id, const uint8_t* index, float* output,
                    uint32_t n_tokens, uint32_t flags);
 
+/* ---- one AMM across the GPUs of a box ---------------------------------------------- */
+
+/* The reference spreads one AMM over an input_parallelism x lut_parallelism grid of DPUs
+ * (src/host/parser.cpp:41-42): token slabs (index slabs, pim_lut_host.cpp:109-117) times output-column
+ * slabs (LUT slabs, pim_lut_host.cpp:26-37).  Here a rank is one process with one context on one GPU;
+ * the two axes are two calls.  NCCL carries the exchanges (all-gathers on the context's stream); it is
+ * loaded at run time, so a machine without it gets LUTAMM_EUNSUPPORTED from these calls only.
+ *
+ * lutamm_shard_unique_id: rank 0 makes the 128-byte id (ncclGetUniqueId) and hands it to the other ranks
+ * by whatever channel the launcher has; lutamm_shard_init joins the context to the communicator
+ * (collective: every rank calls it).  Both stand where the reference's allocate_dpu()/allocate_rank()
+ * sized the DPU grid (src/host/dpu_common.h:11-33). */
+#define LUTAMM_SHARD_ID_BYTES 128
+int lutamm_shard_unique_id(char* id /* [LUTAMM_SHARD_ID_BYTES] */);
+int lutamm_shard_init(lutamm_ctx* ctx, int rank, int world, const char* id);
+int lutamm_shard_finalize(lutamm_ctx* ctx);
+
+/* Sharding by output columns (the reference's lut_parallelism axis).  The layer was loaded on this rank
+ * with ITS slab of the table and the bias: columns [rank*N/G, (rank+1)*N/G), output_feature_len = N/G (a
+ * multiple of 16).  `input` holds all n_tokens rows on every rank.  `gathered` is [G][n_tokens][N/G] fp32
+ * on every rank: this rank's kernel writes block `rank` in place and one all-gather fills the others.
+ * That buffer IS the reference's DPU-tiled output (pim_lut_kernel.c:183, test_amm.cpp:193-202) for
+ * lut_parallelism = G, n_stile_size = n_tokens, feature_stile_size = feature_mtile_size = N/G, so a caller
+ * that takes the reference's layout needs no re-layout pass.
+ * search_mode: every rank searches all tokens, or each rank searches n_tokens/G of them and the uint8
+ * indices are all-gathered (n_tokens*CB bytes on the wire instead of G-fold search work; falls back to
+ * the replicated search when n_tokens % G != 0).  Device buffers only. */
+#define LUTAMM_SHARD_SEARCH_REPLICATED 0u
+#define LUTAMM_SHARD_SEARCH_SPLIT      1u
+int lutamm_amm_column_sharded(lutamm_ctx* ctx, int layer_id, const float* input, float* gathered,
+                              uint32_t n_tokens, uint32_t search_mode, uint32_t flags);
+
+/* Sharding by tokens (the reference's input_parallelism axis): weights replicated, rank r owns rows
+ * [r*n/G, (r+1)*n/G) (n_tokens_total % G == 0), nothing is exchanged.  `input_rows` holds this rank's
+ * rows.  gather == 0: `output` is this rank's [n/G][N] block.  gather != 0: `output` is the full
+ * [n_tokens_total][N] on every rank, written in place by one all-gather.  Device buffers only. */
+int lutamm_amm_token_sharded(lutamm_ctx* ctx, int layer_id, const float* input_rows, float* output,
+                             uint32_t n_tokens_total, uint32_t gather, uint32_t flags);
+
 /* ---- plans, tuning, timing ------------------------------------------------------- */
 
 int lutamm_set_plan(lutamm_ctx* ctx, int layer_id, const lutamm_plan* plan);
@@ -239,6 +277,16 @@ int lutamm_tune(lutamm_ctx* ctx, int layer_id, uint32_t n_tokens, lutamm_plan* b
  * compile-time switch (amm_host.cpp:14-26, pim_lut_host.cpp:124-212) as a runtime flag. */
 int lutamm_enable_timing(lutamm_ctx* ctx, int on);
 int lutamm_get_timings(lutamm_ctx* ctx, lutamm_timings* out);
+
+/* The int8 tensor rate of this GPU, measured: every SM issues nothing but tcgen05.mma kind::i8
+ * (128 x 256 x 32 per instruction, both operands on chip) for a few milliseconds.  The denominator for
+ * the tensor-side roofline of the tcgen05 LUT kernel; the reference has no counterpart (its auto-tuner
+ * uses fitted DPU constants, src/tuner/auto_tuner.cpp:121-166).
+ *   tops            10^12 int8 operations (2 per multiply-add) per second, by CUDA events
+ *   mac_per_clk_sm  multiply-adds per SM clock per SM, by one CTA's own cycle counter
+ *   sm_mhz          the SM clock those two figures imply
+ * Any pointer may be NULL. */
+int lutamm_measure_int8_peak(lutamm_ctx* ctx, double* tops, double* mac_per_clk_sm, double* sm_mhz);
 
 /* Kernels of this library launched on this context since creation. */
 uint64_t lutamm_launch_count(const lutamm_ctx* ctx);

@@ -31,8 +31,12 @@ ABI_SYMBOLS = [
     "lutamm_index_calculation", "lutamm_pim_lut", "lutamm_set_plan", "lutamm_get_plan", "lutamm_set_activation", "lutamm_tune",
     "lutamm_enable_timing", "lutamm_get_timings", "lutamm_launch_count",
     "lutamm_amm_static_scratch", "lutamm_static_scratch_last_error", "lutamm_build_lut",
-    "lutamm_load_weights_layout",
+    "lutamm_load_weights_layout", "lutamm_measure_int8_peak",
+    "lutamm_shard_unique_id", "lutamm_shard_init", "lutamm_shard_finalize", "lutamm_amm_column_sharded",
+    "lutamm_amm_token_sharded",
 ]
+SHARD_SEARCH_REPLICATED, SHARD_SEARCH_SPLIT = 0, 1
+SHARD_ID_BYTES = 128
 
 
 class LutAmmError(RuntimeError):
@@ -65,11 +69,11 @@ class Plan(ctypes.Structure):
     _fields_ = [("variant", ctypes.c_uint32), ("ccs_tokens", ctypes.c_uint32), ("gather_cfg", ctypes.c_uint32),
                 ("umma_n_tile", ctypes.c_uint32), ("umma_split", ctypes.c_uint32), ("umma_stages", ctypes.c_uint32),
                 ("umma_groups", ctypes.c_uint32), ("umma_operand", ctypes.c_uint32),
-                ("umma_sps", ctypes.c_uint32), ("umma_mma_warps", ctypes.c_uint32)]
+                ("umma_sps", ctypes.c_uint32), ("reserved", ctypes.c_uint32)]
 
     def as_dict(self):
         return {k: getattr(self, k) for k in ("variant", "ccs_tokens", "gather_cfg", "umma_n_tile", "umma_split",
-                                              "umma_stages", "umma_groups", "umma_operand", "umma_sps", "umma_mma_warps")}
+                                              "umma_stages", "umma_groups", "umma_operand", "umma_sps")}
 
 
 class Timings(ctypes.Structure):
@@ -116,6 +120,13 @@ def load_library() -> ctypes.CDLL:
     L.lutamm_tune.argtypes = [vp, i32, u32, ctypes.POINTER(Plan)]
     L.lutamm_enable_timing.argtypes = [vp, i32]
     L.lutamm_get_timings.argtypes = [vp, ctypes.POINTER(Timings)]
+    L.lutamm_shard_unique_id.argtypes = [ctypes.c_char_p]
+    L.lutamm_shard_init.argtypes = [vp, i32, i32, ctypes.c_char_p]
+    L.lutamm_shard_finalize.argtypes = [vp]
+    L.lutamm_amm_column_sharded.argtypes = [vp, i32, vp, vp, u32, u32, u32]
+    L.lutamm_amm_token_sharded.argtypes = [vp, i32, vp, vp, u32, u32, u32]
+    dp = ctypes.POINTER(ctypes.c_double)
+    L.lutamm_measure_int8_peak.argtypes = [vp, dp, dp, dp]
     L.lutamm_launch_count.argtypes = [vp]
     L.lutamm_launch_count.restype = ctypes.c_uint64
     L.lutamm_amm_static_scratch.argtypes = [i32, vp, vp, vp, vp, vp, vp, ctypes.POINTER(IndexCalcParams),
@@ -286,6 +297,41 @@ class LutAmmContext:
         M = int(n_tokens if n_tokens is not None else input_index.shape[0])
         self._check(self._L.lutamm_pim_lut(self._h, layer_id, _ptr(input_index), _ptr(output_tensor), M, flags))
 
+    # -- one AMM across the GPUs of a box (one process per GPU)
+    def shard_init(self, rank: int | None = None, world: int | None = None, group=None):
+        """Join this context to an NCCL communicator of its own over `world` ranks.  The 128-byte id is made on
+        rank 0 and broadcast through torch.distributed (any backend), which must be initialised."""
+        import torch
+        import torch.distributed as dist
+        rank = dist.get_rank(group) if rank is None else rank
+        world = dist.get_world_size(group) if world is None else world
+        buf = ctypes.create_string_buffer(SHARD_ID_BYTES)
+        if rank == 0:
+            rc = self._L.lutamm_shard_unique_id(buf)
+            if rc != OK:
+                raise LutAmmError(rc, self._L.lutamm_last_error(None).decode())
+        dev = torch.device("cuda", self.device) if dist.get_backend(group) == "nccl" else torch.device("cpu")
+        t = torch.frombuffer(bytearray(buf.raw), dtype=torch.uint8).to(dev)
+        dist.broadcast(t, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+        self._check(self._L.lutamm_shard_init(self._h, rank, world, bytes(t.cpu().numpy().tobytes())))
+        self.rank, self.world = rank, world
+
+    def shard_finalize(self):
+        self._check(self._L.lutamm_shard_finalize(self._h))
+
+    def amm_column_sharded(self, layer_id: int, input_tensor, gathered, n_tokens: int | None = None,
+                           search_mode: int = SHARD_SEARCH_REPLICATED, flags: int = 0):
+        """This rank's column slab of the AMM into block `rank` of gathered [G][n_tokens][N/G], then one in-place
+        all-gather (the lut_parallelism axis of the reference, pim_lut_host.cpp:26-37)."""
+        M = int(n_tokens if n_tokens is not None else input_tensor.shape[0])
+        self._check(self._L.lutamm_amm_column_sharded(self._h, layer_id, _ptr(input_tensor), _ptr(gathered), M, search_mode, flags))
+
+    def amm_token_sharded(self, layer_id: int, input_rows, output, n_tokens_total: int, gather: bool = False, flags: int = 0):
+        """This rank's tokens of the AMM (the input_parallelism axis, pim_lut_host.cpp:109-117); with gather=True
+        `output` is the full [n_tokens_total][N] on every rank."""
+        self._check(self._L.lutamm_amm_token_sharded(self._h, layer_id, _ptr(input_rows), _ptr(output), n_tokens_total,
+                                                     1 if gather else 0, flags))
+
     # -- plans / tuning / timing
     def set_plan(self, layer_id: int, **kw):
         p = Plan()
@@ -306,6 +352,12 @@ class LutAmmContext:
         p = Plan()
         self._check(self._L.lutamm_tune(self._h, layer_id, n_tokens, ctypes.byref(p)))
         return p.as_dict()
+
+    def measure_int8_peak(self) -> dict:
+        """The GPU's int8 tensor rate, measured by a few milliseconds of nothing but tcgen05.mma kind::i8."""
+        tops, mac, mhz = ctypes.c_double(), ctypes.c_double(), ctypes.c_double()
+        self._check(self._L.lutamm_measure_int8_peak(self._h, ctypes.byref(tops), ctypes.byref(mac), ctypes.byref(mhz)))
+        return {"tops": tops.value, "mac_per_clk_sm": mac.value, "sm_mhz": mhz.value}
 
     def enable_timing(self, on: bool = True):
         self._check(self._L.lutamm_enable_timing(self._h, 1 if on else 0))

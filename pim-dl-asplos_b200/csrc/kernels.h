@@ -57,7 +57,6 @@ struct UmmaPlan {
     uint32_t groups;    // one-hot builder groups of four warps (0 = default)
     uint32_t sps;       // 128-byte slabs a one-hot builder group takes per turn: 1 or 2 (0 = by ring depth)
     uint32_t max_ctas;  // persistent grid size cap: the SM count
-    uint32_t mma_warps; // MMA-issuing warps, 2 or 4 (0 = by tile width)
 };
 bool umma_supported(uint32_t CB, uint32_t CT, uint32_t N);
 bool umma_tile_ok(uint32_t n_tile, bool a_tmem);
@@ -90,6 +89,11 @@ cudaError_t launch_lut_build(const LutBuildArgs& a, cudaStream_t s, const char**
 // LUT in the reference's DPU layout (re-tiled along the output features, tile width T) -> canonical.
 cudaError_t launch_lut_untile(const int8_t* dpu, int8_t* canonical, uint32_t rows, uint32_t N, uint32_t T,
                               cudaStream_t s, const char** why);
+
+// ---- measurement aid: the int8 tensor rate itself --------------------------------------
+// `slabs` x four 128 x n_tile x 32 instructions per CTA, `grid` CTAs; the cycles CTA 0 took land in *d_cycles.
+cudaError_t launch_int8_peak(uint32_t n_tile, uint32_t slabs, uint32_t grid, unsigned long long* d_cycles, uint32_t* dev_err,
+                             cudaStream_t s, const char** why);
 
 // Driver entry point for tensor-map encoding, resolved through the runtime so the library
 // carries no link-time dependency on the driver and loads on machines without one.

@@ -21,14 +21,14 @@
 //
 //   warp 0        TMA producer: B slabs = LUT^T[n0:n0+N_TILE][k:k+128] (K-major, 128-byte
 //                 swizzle) from the load-time transposed copy of the LUT
-//   warps 1..W    issue tcgen05.mma, 4 per slab, slab x by warp 1 + x % W (one elected lane), W = 2 or 4;
+//   warps 1-2     issue tcgen05.mma, 4 per slab, slab x by warp 1 + x % 2 (one elected lane);
 //                 warp 1 also owns TMEM (alloc/dealloc)
-//   next 16       build the one-hot A slab straight from the uint8 indices (it never exists in
+//   warps 3-18    build the one-hot A slab straight from the uint8 indices (it never exists in
 //                 HBM): four groups of four warps, group k taking every fourth slab, one tile
 //                 row per thread, the row's eight 16-byte chunks read from a one-hot table in
 //                 shared memory.  Four groups because a slab is a chain of latencies (index
 //                 load, wait, fence, arrive): they have to overlap across slabs.
-//   last 4        epilogue: TMEM -> registers -> shared-memory transpose -> dequantise ->
+//   warps 19-22   epilogue: TMEM -> registers -> shared-memory transpose -> dequantise ->
 //                 row-contiguous 16-byte global stores (each warp owns one 32-lane quadrant);
 //                 clears the accumulator behind itself
 //
@@ -37,18 +37,6 @@
 #include "kernels.h"
 #include "ptx.cuh"
 #include "epilogue.cuh"
-
-#ifdef LUTAMM_TRACE
-// experiment only: clock stamps of CTA 0, [slab][event]
-__device__ unsigned long long g_trace[256 * 8];
-extern "C" int lutamm_exp_read_trace(unsigned long long* out) { return (int)cudaMemcpyFromSymbol(out, g_trace, sizeof(g_trace)); }
-#ifndef LUTAMM_TRACE_CTA
-#define LUTAMM_TRACE_CTA 0
-#endif
-#define TRACE(sl, e) do { if (blockIdx.x == LUTAMM_TRACE_CTA && (sl) < 256u) g_trace[(sl) * 8 + (e)] = clock64(); } while (0)
-#else
-#define TRACE(sl, e) do { } while (0)
-#endif
 
 namespace lutamm {
 
@@ -60,14 +48,9 @@ constexpr uint32_t kABytes = kMTile * kSlabK;  // 16 KiB
 constexpr uint32_t kMaxAgenGroups = 4;  // each group: 4 warps = 128 rows (more groups measured slower)
 constexpr uint32_t kEpiWarps = 4;
 constexpr uint32_t kEpiThreads = kEpiWarps * 32;
-// MMA-issuing warps: slab x of the CTA's sequence is issued by warp x % W, W = 2 or 4.  Measured with
-// nothing else running (one elected lane per warp issuing four-instruction slabs back to back, operand A
-// in tensor memory): one warp sustains a slab per 234 / 309 / 414 cycles at N = 64 / 128 / 192, four
-// warps 146 / 274 / 400 - the pipe's own 2 N cycles plus about 16.  With A in shared memory the same
-// loop needs 233 / 317 / 445 cycles: A and B together then saturate the 128 bytes per clock of shared
-// memory.
-constexpr uint32_t kMaxMmaWarps = 4;
-constexpr uint32_t kMaxThreads = (1 + kMaxMmaWarps + 4 * kMaxAgenGroups + kEpiWarps) * 32;  // 800
+constexpr uint32_t kMmaWarps = 2;      // MMA-issuing warps: slab x of the CTA's sequence is issued by warp x % 2
+constexpr uint32_t kFirstAgenWarp = 1 + kMmaWarps;
+constexpr uint32_t kMaxThreads = (kFirstAgenWarp + 4 * kMaxAgenGroups + kEpiWarps) * 32;  // 736
 constexpr uint32_t kMaxASlots = 8;    // one-hot slabs in flight (tensor memory: 32 columns each)
 constexpr uint32_t kMaxBSlots = 16;   // LUT slabs in flight (shared memory)
 constexpr uint32_t kNumBarriers = 2 * kMaxASlots + 2 * kMaxBSlots + 4;
@@ -89,7 +72,6 @@ struct UmmaParams {
     uint32_t tiles_m, tiles_n;
     uint32_t log2_ct;
     uint32_t groups;         // A-builder groups (1..4); a_slots % (groups * slabs per turn) == 0
-    uint32_t mma_warps;      // MMA-issuing warps (2 or 4); both ring depths are multiples of it
     int32_t* acc_scratch;    // [split][M][N] int32 partial sums (split > 1); needs no initialisation
     uint32_t* tile_counters;
     uint32_t* dev_err;
@@ -132,7 +114,7 @@ __device__ __forceinline__ Item decode_item(const UmmaParams& p, uint32_t item, 
     return it;
 }
 
-template <uint32_t N_TILE, bool A_TMEM>
+template <uint32_t N_TILE, bool A_TMEM, uint32_t SPS>
 __global__ void __launch_bounds__(kMaxThreads, 1)
 lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const UmmaParams p) {
     constexpr uint32_t kBBytes = N_TILE * kSlabK;
@@ -165,8 +147,6 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t n_items = p.tiles_m * p.tiles_n * p.split;
     const uint32_t kAgenGroups = p.groups;
-    const uint32_t kMmaWarps = p.mma_warps;
-    const uint32_t kFirstAgenWarp = 1 + kMmaWarps;
     const uint32_t kFirstEpiWarp = kFirstAgenWarp + 4 * kAgenGroups;
 
     if (threadIdx.x == 0) {
@@ -212,44 +192,28 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
     tc_fence_after_sync();
 
     if (warp == 0) {
-        // ---------------- TMA producers (the LUT never depends on the preceding kernel)
-        // One thread's turn - barrier query, expect_tx, the copy instruction - is a chain of round trips
-        // of about 400 cycles however small the tile (measured: one issuing thread sustains one tensor
-        // copy per ~340 cycles for boxes of 64 to 256 rows alike, two threads twice and four threads four
-        // times that), which is more than a slab's MMA time at every tile width below 192.  So P = W lanes
-        // of this warp run the loop in lockstep, lane l taking slabs x = l (mod P) of the CTA's sequence:
-        // one instruction issue serves P slabs.  The LUT ring is a multiple of P deep, so a lane always
-        // refills the same slots.
-        const uint32_t P = kMmaWarps;
-        if (lane < P) {
-            uint32_t j = lane, ph = 0, x0 = 0;  // LUT slot and phase bit of this lane's next slab; slabs before the item
+        // ---------------- TMA producer (the LUT never depends on the preceding kernel)
+        if (lane == 0) {
+            uint32_t j = 0, ph = 0;  // LUT slot and the phase bit of its current use
             bool ok = true;
             for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
                 const Item it = decode_item(p, item, N_TILE);
-                for (uint32_t i = (lane - x0) & (P - 1u); i < it.nslab; i += P) {
+                for (uint32_t i = 0; i < it.nslab; ++i) {
                     ok = mbar_wait<32>(b_empty0 + 8 * j, ph ^ 1, s_abort);
                     if (!ok) break;
-#ifdef LUTAMM_EXP_SKIP_TMA
-                    if (x0 + i >= SB) { mbar_arrive(b_full0 + 8 * j); } else
-#endif
-                    {
                     mbar_arrive_expect_tx(b_full0 + 8 * j, kBBytes);
                     tma_load_2d(smem_u32(s_b + (size_t)j * kBBytes), &lut_t_map, b_full0 + 8 * j,
                                 (int32_t)((it.slab_begin + i) * kSlabK), (int32_t)it.n0);
-                    }
-                    TRACE(it.slab_begin + i, 0);
-                    j += P;
-                    if (j >= SB) { j -= SB; ph ^= 1; }
+                    if (++j == SB) { j = 0; ph ^= 1; }
                 }
-                x0 += it.nslab;
             }
         }
         __syncwarp();
     } else if (warp < kFirstAgenWarp) {
-        // ---------------- MMA issuers: W warps, slab x of the CTA's sequence goes to warp x % W.
+        // ---------------- MMA issuers: two warps, slab x of the CTA's sequence goes to warp x % 2.
         // A slab's turn (barrier probes, fence, election, four tcgen05.mma of 32 bytes of K each, one
-        // commit per ring) costs the issuing warp 600 to 800 cycles, more than the four MMAs take to
-        // execute; several warps taking turns keep the tensor pipe fed.  All MMAs accumulate into an
+        // commit per ring) costs the issuing warp about 600 cycles, more than the four MMAs take to
+        // execute; two warps taking turns keep the tensor pipe fed.  All MMAs accumulate into an
         // accumulator the epilogue left at zero, integer addition commutes, so the order in which
         // the two warps' instructions reach the pipe does not matter.  Each warp walks its loop
         // converged (waits and descriptor arithmetic stay warp-uniform; a lone lane running the
@@ -275,32 +239,22 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
                 if (!ok) break;
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + ab * N_TILE;
-                // this warp's slabs are those with (x0 + i) % W == me; W is a power of two
-                for (uint32_t i = (me - x0) & (kMmaWarps - 1u); i < it.nslab; i += kMmaWarps) {
+                for (uint32_t i = (x0 + me) & 1u; i < it.nslab; i += 2) {
                     const uint32_t x = x0 + i;
                     a_slot(x, k, pa);
-#ifndef LUTAMM_TRACE_BLD
-                    if (lane == 0) TRACE(x, 1);
-#endif
                     if (!ready) {
                         ok = mbar_wait(b_full0 + 8 * j, pb, s_abort) && mbar_wait(a_full0 + 8 * k, pa, s_abort);
                         if (!ok) break;
                     }
-                    uint32_t j2 = j + kMmaWarps, pb2 = pb;
+                    uint32_t j2 = j + 2, pb2 = pb;
                     if (j2 >= SB) { j2 -= SB; pb2 ^= 1; }
                     uint32_t k2, pa2;
-                    a_slot(x + kMmaWarps, k2, pa2);
-#ifndef LUTAMM_TRACE_BLD
-                    if (lane == 0) TRACE(x, 2);
-#endif
+                    a_slot(x + 2, k2, pa2);
                     const bool next_ready = mbar_test2(b_full0 + 8 * j2, pb2, a_full0 + 8 * k2, pa2);
                     tc_fence_after_sync();
                     if (elect_one()) {
                         // descriptors differ from slot 0's only in the 16-byte-unit address field
                         const uint32_t b_lo = b_lo0 + j * (kBBytes >> 4);
-#ifdef LUTAMM_EXP_SKIP_MMA
-                        if (x < SA)
-#endif
                         if constexpr (A_TMEM) {
                             const uint32_t ta = tmem_base + kATmemBase + k * 32;
 #pragma unroll
@@ -317,9 +271,6 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
                         umma_commit(b_empty0 + 8 * j);
                     }
                     __syncwarp();
-#ifndef LUTAMM_TRACE_BLD
-                    if (lane == 0) TRACE(x, 3);
-#endif
                     j = j2; pb = pb2;
                     ready = next_ready;
                 }
@@ -354,134 +305,113 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
             else v.x = __ldcg(q);
             return v;
         };
-        // Row of the one-hot table per 16-byte chunk, then one conflict-free 16-byte load each.  An index
-        // that is out of range for its chunk selects the all-zero row (the indices may come from a
-        // caller, not only from the search kernel).
-        auto build_row = [&](const uint4& raw, uint32_t slab, uint4 (&chunk)[8]) {
-            if (lg == 4) {  // one codebook == one 16-byte chunk
-#pragma unroll
-                for (uint32_t j = 0; j < 8; ++j) {
-                    const uint32_t ix = ((j < 4 ? raw.x : raw.y) >> (8 * (j & 3))) & 0xFFu;
-#ifdef LUTAMM_ONEHOT_ALU
-                    chunk[j] = onehot16(ix);
-#else
-                    chunk[j] = *reinterpret_cast<const uint4*>(tab_lane + min(ix, 16u) * 128);
-#endif
-                }
-            } else if (lg == 3) {  // two codebooks per chunk: low eight bytes, high eight bytes
-                const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-                for (uint32_t j = 0; j < 8; ++j) {
-                    const uint32_t two = (w[j >> 1] >> (16 * (j & 1))) & 0xFFFFu;
-                    const uint32_t i0 = two & 0xFFu, i1 = two >> 8;
-                    const uint4 lo = *reinterpret_cast<const uint4*>(tab_lane + (i0 < 8u ? i0 : 16u) * 128);
-                    const uint4 hi = *reinterpret_cast<const uint4*>(tab_lane + (i1 < 8u ? i1 + 8u : 16u) * 128);
-                    chunk[j] = make_uint4(lo.x | hi.x, lo.y | hi.y, lo.z | hi.z, lo.w | hi.w);
-                }
-            } else {  // a codebook spans CT/16 chunks
-#pragma unroll
-                for (uint32_t j = 0; j < 8; ++j) {
-                    const uint32_t k0 = slab * kSlabK + 16 * j;
-                    const uint32_t ix = (raw.x >> (8 * (j >> (lg - 4)))) & 0xFFu;  // CT >= 128: always byte 0
-                    const uint32_t sub = (k0 & (CT - 1)) >> 4;
-                    chunk[j] = *reinterpret_cast<const uint4*>(tab_lane + ((ix >> 4) == sub ? (ix & 15u) : 16u) * 128);
-                }
-            }
-        };
-        // Slab x of the CTA's sequence goes to group x % groups and to one-hot slot x % SA.  A turn is
-        // software-pipelined: the row of the group's NEXT slab is looked up while the store of the
-        // current one is in flight - a warp's tcgen05.st of 32 columns takes about 290 cycles to
-        // complete (measured alone), and the look-up phase is of the same order under load - and only
-        // then is the store waited for and the slab handed to the MMA warps.
+        // A group takes SPS consecutive slabs per turn: the fixed cost of a turn - the fences, the
+        // arrival, the loop itself, a chain of latencies of many hundred cycles for a lone warp - is
+        // then paid once per batch.  Batch q of the CTA's sequence goes to group q % groups; slab x of
+        // the sequence uses one-hot slot x % SA.
+        constexpr uint32_t kBatch = SPS;
         // Index bytes are fetched kPrefetch turns ahead: with the LUT tiles streaming through the same
         // L2 a load takes a good part of a turn.
-#ifdef LUTAMM_EXP_PREFETCH
-        constexpr uint32_t kPrefetch = LUTAMM_EXP_PREFETCH;
-#else
         constexpr uint32_t kPrefetch = 2;
-#endif
         const uint32_t sa_magic = p.a_slots_magic;
-        uint32_t ga = 0;  // slabs of the CTA before the current item
+        uint32_t ga = 0, qb = 0;  // slabs and batches of the CTA before the current item
         bool ok = true;
         for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
             const Item it = decode_item(p, item, N_TILE);
             const uint8_t* grow = a.idx + (size_t)min(it.m0 + r, a.M - 1) * a.CB;  // rows past M: masked in the epilogue
-            uint32_t i = (grp + kAgenGroups - (ga % kAgenGroups)) % kAgenGroups;  // this group's first slab of the item
-            const uint32_t stride = kAgenGroups;
-            uint4 raw_q[kPrefetch];
+            uint32_t i = kBatch * ((grp + kAgenGroups - (qb % kAgenGroups)) % kAgenGroups);  // first slab of the turn
+            const uint32_t stride = kBatch * kAgenGroups;
+            uint4 raw_q[kPrefetch][kBatch];
 #pragma unroll
-            for (uint32_t k = 0; k < kPrefetch; ++k) {
-                raw_q[k] = make_uint4(0, 0, 0, 0);
-                if (i + k * stride < it.nslab) raw_q[k] = load_raw(grow, it.slab_begin + i + k * stride);
-            }
-            uint4 chunk[8];
-            if (i < it.nslab) build_row(raw_q[0], it.slab_begin + i, chunk);
-            for (; i < it.nslab && ok; i += stride) {
-                const uint32_t x = ga + i, xq = div_magic(x, sa_magic), k = x - xq * SA, pa = xq & 1u;
-                // The row is in registers before the slot is waited for: what follows the wait is on the
-                // slot's turn-around path.  The whole warp polls (one broadcast access), so it stays converged.
-                if ((warp & 3u) == 0 && lane == 0) TRACE(x, 4);
-                ok = mbar_wait(a_empty0 + 8 * k, pa ^ 1, s_abort);
-                if (!ok) break;
-                if ((warp & 3u) == 0 && lane == 0) TRACE(x, 5);
-                if constexpr (A_TMEM) {
-                    tc_fence_after_sync();
-                    // the row goes to this warp's lane quadrant of tensor memory, K bytes in column order
-                    uint32_t w[32];
+            for (uint32_t k = 0; k < kPrefetch; ++k)
 #pragma unroll
-                    for (uint32_t j = 0; j < 8; ++j) {
-                        w[4 * j + 0] = chunk[j].x; w[4 * j + 1] = chunk[j].y; w[4 * j + 2] = chunk[j].z; w[4 * j + 3] = chunk[j].w;
-                    }
-#ifdef LUTAMM_EXP_SKIP_ST
-                    if (x < SA)
-#endif
-                    tmem_st_32x32b_x32(tmem_base + (((warp & 3u) * 32u) << 16) + kATmemBase + k * 32, w);
-                } else {
-                    unsigned char* row_ptr = s_a + (size_t)k * kABytes + r * kSlabK;
-#pragma unroll
-                    for (uint32_t j = 0; j < 8; ++j)  // 128-byte swizzle: 16-byte chunk j of row r lands at j ^ (r & 7)
-                        *reinterpret_cast<uint4*>(row_ptr + ((j ^ sw) << 4)) = chunk[j];
+                for (uint32_t b = 0; b < kBatch; ++b) {
+                    raw_q[k][b] = make_uint4(0, 0, 0, 0);
+                    if (i + k * stride + b < it.nslab) raw_q[k][b] = load_raw(grow, it.slab_begin + i + k * stride + b);
                 }
-#ifdef LUTAMM_TRACE_BLD
-                if ((warp & 3u) == 0 && lane == 0) TRACE(x, 1);
-#endif
-                // next turn's row while this one's store completes
+            for (; i < it.nslab && ok; i += stride) {
+                uint4 raw[kBatch];
 #pragma unroll
-                for (uint32_t q = 0; q + 1 < kPrefetch; ++q) raw_q[q] = raw_q[q + 1];
-                raw_q[kPrefetch - 1] = make_uint4(0, 0, 0, 0);
-                if (i + kPrefetch * stride < it.nslab)
-                    raw_q[kPrefetch - 1] = load_raw(grow, it.slab_begin + i + kPrefetch * stride);
-#ifndef LUTAMM_EXP_NOPIPE
-#ifdef LUTAMM_EXP_SKIP_LDS
-                if (x < SA)
-#endif
-                if (i + stride < it.nslab) build_row(raw_q[0], it.slab_begin + i + stride, chunk);
-#endif
-#ifdef LUTAMM_TRACE_BLD
-                asm volatile("" :: "r"(chunk[0].x), "r"(chunk[1].x), "r"(chunk[2].x), "r"(chunk[3].x), "r"(chunk[4].x), "r"(chunk[5].x), "r"(chunk[6].x), "r"(chunk[7].x));
-                if ((warp & 3u) == 0 && lane == 0) TRACE(x, 2);
-#endif
-#ifdef LUTAMM_EXP_SKIP_FENCE
-                if (x < SA)
-#endif
+                for (uint32_t b = 0; b < kBatch; ++b) {
+                    raw[b] = raw_q[0][b];
+#pragma unroll
+                    for (uint32_t k = 0; k + 1 < kPrefetch; ++k) raw_q[k][b] = raw_q[k + 1][b];
+                    if (i + kPrefetch * stride + b < it.nslab)
+                        raw_q[kPrefetch - 1][b] = load_raw(grow, it.slab_begin + i + kPrefetch * stride + b);
+                }
+#pragma unroll
+                for (uint32_t b = 0; b < kBatch; ++b) {
+                    if (i + b >= it.nslab) continue;  // an odd last batch
+                    const uint32_t slab = it.slab_begin + i + b;
+                    const uint32_t x = ga + i + b, xq = div_magic(x, sa_magic), k = x - xq * SA, pa = xq & 1u;
+                    // Row of the one-hot table per 16-byte chunk, then one conflict-free 16-byte load each.
+                    // An index that is out of range for its chunk selects the all-zero row (the indices
+                    // may come from a caller, not only from the search kernel).
+                    uint4 chunk[8];
+                    if (lg == 4) {  // one codebook == one 16-byte chunk
+#pragma unroll
+                        for (uint32_t j = 0; j < 8; ++j) {
+                            const uint32_t ix = ((j < 4 ? raw[b].x : raw[b].y) >> (8 * (j & 3))) & 0xFFu;
+                            chunk[j] = *reinterpret_cast<const uint4*>(tab_lane + min(ix, 16u) * 128);
+                        }
+                    } else if (lg == 3) {  // two codebooks per chunk: low eight bytes, high eight bytes
+                        const uint32_t w[4] = {raw[b].x, raw[b].y, raw[b].z, raw[b].w};
+#pragma unroll
+                        for (uint32_t j = 0; j < 8; ++j) {
+                            const uint32_t two = (w[j >> 1] >> (16 * (j & 1))) & 0xFFFFu;
+                            const uint32_t i0 = two & 0xFFu, i1 = two >> 8;
+                            const uint4 lo = *reinterpret_cast<const uint4*>(tab_lane + (i0 < 8u ? i0 : 16u) * 128);
+                            const uint4 hi = *reinterpret_cast<const uint4*>(tab_lane + (i1 < 8u ? i1 + 8u : 16u) * 128);
+                            chunk[j] = make_uint4(lo.x | hi.x, lo.y | hi.y, lo.z | hi.z, lo.w | hi.w);
+                        }
+                    } else {  // a codebook spans CT/16 chunks
+#pragma unroll
+                        for (uint32_t j = 0; j < 8; ++j) {
+                            const uint32_t k0 = slab * kSlabK + 16 * j;
+                            const uint32_t ix = (raw[b].x >> (8 * (j >> (lg - 4)))) & 0xFFu;  // CT >= 128: always byte 0
+                            const uint32_t sub = (k0 & (CT - 1)) >> 4;
+                            chunk[j] = *reinterpret_cast<const uint4*>(tab_lane + ((ix >> 4) == sub ? (ix & 15u) : 16u) * 128);
+                        }
+                    }
+                    // The row is in registers before the slot is waited for: what follows the wait is on
+                    // the slot's turn-around path.  The whole warp polls (one broadcast access), so it
+                    // stays converged.
+                    ok = ok && mbar_wait(a_empty0 + 8 * k, pa ^ 1, s_abort);
+                    if (!ok) continue;
+                    if constexpr (A_TMEM) {
+                        tc_fence_after_sync();
+                        // the row goes to this warp's lane quadrant of tensor memory, K bytes in column order
+                        uint32_t w[32];
+#pragma unroll
+                        for (uint32_t j = 0; j < 8; ++j) {
+                            w[4 * j + 0] = chunk[j].x; w[4 * j + 1] = chunk[j].y; w[4 * j + 2] = chunk[j].z; w[4 * j + 3] = chunk[j].w;
+                        }
+                        tmem_st_32x32b_x32(tmem_base + (((warp & 3u) * 32u) << 16) + kATmemBase + k * 32, w);
+                    } else {
+                        unsigned char* row_ptr = s_a + (size_t)k * kABytes + r * kSlabK;
+#pragma unroll
+                        for (uint32_t j = 0; j < 8; ++j)  // 128-byte swizzle: 16-byte chunk j of row r lands at j ^ (r & 7)
+                            *reinterpret_cast<uint4*>(row_ptr + ((j ^ sw) << 4)) = chunk[j];
+                    }
+                }
                 if constexpr (A_TMEM) {
                     tmem_st_wait();
-#ifdef LUTAMM_TRACE_BLD
-                    if ((warp & 3u) == 0 && lane == 0) TRACE(x, 3);
-#endif
                     tc_fence_before_sync();
                 } else {
                     fence_proxy_async_smem();
                 }
                 __syncwarp();
-                if ((warp & 3u) == 0 && lane == 0) TRACE(x, 6);
-                if (lane == 0) mbar_arrive(a_full0 + 8 * k);
-                if ((warp & 3u) == 0 && lane == 0) TRACE(x, 7);
-#ifdef LUTAMM_EXP_NOPIPE
-                if (i + stride < it.nslab) build_row(raw_q[0], it.slab_begin + i + stride, chunk);
-#endif
+                if (lane == 0 && ok) {
+#pragma unroll
+                    for (uint32_t b = 0; b < kBatch; ++b)
+                        if (i + b < it.nslab) {
+                            const uint32_t x = ga + i + b;
+                            mbar_arrive(a_full0 + 8 * (x - div_magic(x, sa_magic) * SA));
+                        }
+                }
             }
             ga += it.nslab;
+            qb += (it.nslab + kBatch - 1) / kBatch;
         }
     } else {
         // ---------------- epilogue: four warps, each on the TMEM lane quadrant (warp % 4) it may read
@@ -701,9 +631,9 @@ size_t umma_smem_bytes(uint32_t n_tile, uint32_t a_slots, uint32_t b_slots, bool
 constexpr size_t kSmemLimit = 227 * 1024;
 constexpr size_t kSmemOneCtaPerSm = 116 * 1024;  // of 228 KiB per SM
 
-template <uint32_t N_TILE, bool A_TMEM>
+template <uint32_t N_TILE, bool A_TMEM, uint32_t SPS>
 cudaError_t run(const CUtensorMap& map, const UmmaParams& p, uint32_t grid, size_t smem, cudaStream_t s) {
-    auto k = lut_onehot_umma_kernel<N_TILE, A_TMEM>;
+    auto k = lut_onehot_umma_kernel<N_TILE, A_TMEM, SPS>;
     // Never two of these CTAs on one SM: the second would sit in tcgen05.alloc until the first has
     // freed its tensor memory, and with split tiles the first may be waiting for the second's slice.
     // The grid is at most one CTA per SM, but while the preceding kernel still holds some SMs
@@ -714,7 +644,7 @@ cudaError_t run(const CUtensorMap& map, const UmmaParams& p, uint32_t grid, size
     if (e != cudaSuccess) return e;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3((1 + p.mma_warps + 4 * p.groups + kEpiWarps) * 32);
+    cfg.blockDim = dim3((kFirstAgenWarp + 4 * p.groups + kEpiWarps) * 32);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = s;
     cudaLaunchAttribute attr[1];
@@ -728,23 +658,23 @@ cudaError_t run(const CUtensorMap& map, const UmmaParams& p, uint32_t grid, size
 // Ring depths.  One-hot slots: an even number (two warps issue alternate slabs); in tensor memory what the
 // two accumulators leave of the 512 columns, 32 columns a slab; in shared memory as many as leave the
 // LUT ring at least as deep.  LUT slots: whatever shared memory still holds.
-void ring_depths(uint32_t n_tile, bool a_tmem, uint32_t want_b, uint32_t W, uint32_t* a_slots, uint32_t* b_slots) {
+void ring_depths(uint32_t n_tile, bool a_tmem, uint32_t want_b, uint32_t* a_slots, uint32_t* b_slots) {
     uint32_t sa = kMaxASlots;
     if (a_tmem) {
         const uint32_t room = (512u - 2 * n_tile) / 32u;
-        if (sa > room) sa = room - room % W;
+        if (sa > room) sa = room & ~1u;
     } else {
-        while (sa > W && umma_smem_bytes(n_tile, sa, sa, false) > kSmemLimit) sa -= W;
+        while (sa > 2 && umma_smem_bytes(n_tile, sa, sa, false) > kSmemLimit) sa -= 2;
     }
     uint32_t sb = kMaxBSlots;
     while (sb > sa && umma_smem_bytes(n_tile, sa, sb, a_tmem) > kSmemLimit) --sb;
-    if (want_b && want_b < sb) sb = want_b < W ? W : want_b;
-    // Both rings hold a multiple of W slots: the W MMA-issuing warps take slabs in rotation, so with such
-    // a ring every slot is always consumed by the same warp, whose program order then guarantees that
+    if (want_b && want_b < sb) sb = want_b < 2 ? 2 : want_b;
+    // Both rings hold an even number of slots: the two MMA-issuing warps take alternate slabs, so with an
+    // even ring every slot is always consumed by the same warp, whose program order then guarantees that
     // a slot's previous use was waited for before the next one is asked about.  (An mbarrier parity wait
     // tells only two consecutive phases apart: asked about use q while use q-1 is still outstanding, it
     // answers for use q-2.)
-    sb -= sb % W;
+    sb &= ~1u;
     if (sa > sb) sa = sb;
     *a_slots = sa;
     *b_slots = sb;
@@ -788,7 +718,7 @@ uint32_t umma_auto_split(uint32_t M, uint32_t CB, uint32_t CT, uint32_t N, uint3
 //    256-wide tiles at 65536 x 4096 -> 16384, which stays available as a plan option);
 //  * fewer tiles than SMs: 128-wide tiles and the codebook axis split across CTAs until the SMs are
 //    covered.
-// operand / n_tile != 0 force that choice.
+// operand / n_tile / sps != 0 force that choice.
 void umma_default_plan(uint32_t M, uint32_t CB, uint32_t CT, uint32_t N, int sm_count, uint32_t operand,
                        uint32_t n_tile, uint32_t sps, UmmaPlan* p) {
     const uint32_t tm = (M + kMTile - 1) / kMTile;
@@ -812,9 +742,8 @@ void umma_default_plan(uint32_t M, uint32_t CB, uint32_t CT, uint32_t N, int sm_
     p->split = umma_auto_split(M, CB, CT, N, n_tile, sm_count);
     p->stages = 0;
     p->groups = 0;
-    p->sps = sps;  // accepted, not used: a builder group takes one slab per turn
+    p->sps = sps;  // 0: chosen at launch from the ring depth
     p->max_ctas = (uint32_t)sm_count;
-    p->mma_warps = 0;  // chosen at launch from the tile width
 }
 
 cudaError_t umma_make_tmap(CUtensorMap* out, const int8_t* lut_t, uint32_t CB, uint32_t CT, uint32_t N,
@@ -854,11 +783,12 @@ cudaError_t launch_umma(const LutArgs& a, const CUtensorMap& lut_t_map, const Um
     p.slabs_per_item = (p.slabs_total + split - 1) / split;
     split = (p.slabs_total + p.slabs_per_item - 1) / p.slabs_per_item;  // no empty slices
     p.split = split;
-    p.mma_warps = plan.mma_warps == 2 ? 2u : plan.mma_warps == 4 ? 4u : (plan.n_tile <= 160 ? 4u : 2u);
-    if (a_tmem && (512u - 2 * plan.n_tile) / 32u < p.mma_warps) p.mma_warps = 2;
-    ring_depths(plan.n_tile, a_tmem, plan.stages, p.mma_warps, &p.a_slots, &p.b_slots);
+    ring_depths(plan.n_tile, a_tmem, plan.stages, &p.a_slots, &p.b_slots);
     if (p.a_slots < 2 || p.b_slots < 2) { *why = "tcgen05 variant: this tile leaves room for fewer than two slabs in flight"; return cudaErrorInvalidValue; }
     p.a_slots_magic = (uint32_t)(((1ull << 32) + p.a_slots - 1) / p.a_slots);
+    // slabs a builder group takes per turn
+    uint32_t sps = plan.sps >= 2 ? 2u : 1u;  // one measured at least as fast as two on every benchmark shape
+    if (sps > p.a_slots / 2 || plan.n_tile == 160) sps = 1;  // (160-wide tiles are built for one slab per turn)
     p.tiles_m = (a.M + kMTile - 1) / kMTile;
     p.tiles_n = (a.N + plan.n_tile - 1) / plan.n_tile;
     p.log2_ct = 0;
@@ -871,26 +801,36 @@ cudaError_t launch_umma(const LutArgs& a, const CUtensorMap& lut_t_map, const Um
     // only two consecutive phases apart, and groups do not wait for one another - with the slots rotating
     // through the groups, one group two uses ahead of a stalled one would take the stalled group's
     // still-pending phase for its own and overwrite a slab that was never consumed.  Slab x goes to group
-    // x % groups and to slot x % slots, so the condition is slots % groups == 0: take the largest such
-    // group count not above the one asked for.
+    // (x / sps) % groups and to slot x % slots, so the condition is slots % (groups * sps) == 0: take the
+    // largest such group count not above the one asked for.
     p.groups = plan.groups ? (plan.groups > kMaxAgenGroups ? kMaxAgenGroups : plan.groups) : 4;
+    // Two-slab turns are counted per item, slots over the CTA's whole slab sequence: after an item with
+    // an odd number of slabs the pairs would straddle slots differently and the slots would change
+    // hands, so a CTA that takes several items of which any is odd builds one slab per turn.
     const uint64_t items = (uint64_t)p.tiles_m * p.tiles_n * split;
     const uint32_t cap = plan.max_ctas ? plan.max_ctas : 148u;
     const uint32_t grid = (uint32_t)(items < cap ? items : cap);
-    while (p.groups > 1 && p.a_slots % p.groups != 0) --p.groups;
+    if (sps == 2 && items > grid && ((p.slabs_per_item & 1u) || (p.slabs_total & 1u))) sps = 1;
+    while (p.groups > 1 && p.a_slots % (p.groups * sps) != 0) --p.groups;
     if (split > 1 && (!acc_scratch || !tile_counters)) { *why = "tcgen05 variant: split > 1 needs scratch"; return cudaErrorInvalidValue; }
     const size_t smem = umma_smem_bytes(plan.n_tile, p.a_slots, p.b_slots, a_tmem);
-#define LUTAMM_UMMA_CASE(NT, TM) \
-    if (plan.n_tile == NT && a_tmem == TM) return run<NT, TM>(lut_t_map, p, grid, smem, s);
-    LUTAMM_UMMA_CASE(64, true)
-    LUTAMM_UMMA_CASE(128, true)
-    LUTAMM_UMMA_CASE(160, true)
-    LUTAMM_UMMA_CASE(192, true)
-    LUTAMM_UMMA_CASE(64, false)
-    LUTAMM_UMMA_CASE(128, false)
-    LUTAMM_UMMA_CASE(256, false)
+#define LUTAMM_UMMA_CASE(NT, TM, SP) \
+    if (plan.n_tile == NT && a_tmem == TM && sps == SP) return run<NT, TM, SP>(lut_t_map, p, grid, smem, s);
+    LUTAMM_UMMA_CASE(64, true, 1)
+    LUTAMM_UMMA_CASE(64, true, 2)
+    LUTAMM_UMMA_CASE(128, true, 1)
+    LUTAMM_UMMA_CASE(128, true, 2)
+    LUTAMM_UMMA_CASE(160, true, 1)
+    LUTAMM_UMMA_CASE(192, true, 1)
+    LUTAMM_UMMA_CASE(192, true, 2)
+    LUTAMM_UMMA_CASE(64, false, 1)
+    LUTAMM_UMMA_CASE(64, false, 2)
+    LUTAMM_UMMA_CASE(128, false, 1)
+    LUTAMM_UMMA_CASE(128, false, 2)
+    LUTAMM_UMMA_CASE(256, false, 1)
+    LUTAMM_UMMA_CASE(256, false, 2)
 #undef LUTAMM_UMMA_CASE
-    *why = "tcgen05 variant: this tile / operand combination is not built";
+    *why = "tcgen05 variant: this tile / operand / slabs-per-turn combination is not built";
     return cudaErrorInvalidValue;
 }
 

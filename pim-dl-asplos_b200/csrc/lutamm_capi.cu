@@ -4,6 +4,7 @@
 // machine without a usable device gets an error from lutamm_create, never a slow answer.
 #include "../../include/lutamm.h"
 #include "kernels.h"
+#include "nccl_shard.h"
 
 #include <algorithm>
 #include <cstdio>
@@ -81,6 +82,9 @@ struct lutamm_ctx {
     bool last_valid = false;
     uint64_t launches = 0;
     std::string err;
+    // sharding across the GPUs of a box (lutamm_shard_init)
+    lutamm::NcclComm comm = nullptr;
+    int rank = 0, world = 1;
 };
 
 namespace {
@@ -209,7 +213,6 @@ int run_lut(lutamm_ctx* c, Layer& L, const uint8_t* d_idx, float* d_out, int32_t
         up.stages = plan.umma_stages;
         up.groups = plan.umma_groups;
         if (plan.umma_sps) up.sps = plan.umma_sps;
-        up.mma_warps = plan.umma_mma_warps;
         if (!umma_tile_ok(up.n_tile, a_tmem))
             return fail(c, LUTAMM_EINVAL, "umma_n_tile must be 64, 128 or 256 with the one-hot operand in shared memory, "
                                           "64, 128, 160 or 192 with it in tensor memory");
@@ -458,6 +461,8 @@ int lutamm_destroy(lutamm_ctx* c) {
     if (c->s_in) cudaStreamSynchronize(c->s_in);
     cudaStreamSynchronize(c->stream);
     if (c->s_out) cudaStreamSynchronize(c->s_out);
+    if (c->comm && nccl_api().ok) nccl_api().comm_destroy(c->comm);
+    c->comm = nullptr;
     for (auto& kv : c->layers) free_layer(kv.second);
     for (int k = 0; k < 2; ++k) {
         cudaFree(c->p_in[k].p); cudaFree(c->p_out[k].p);
@@ -695,8 +700,6 @@ int lutamm_set_plan(lutamm_ctx* c, int layer_id, const lutamm_plan* plan) {
                                       "0, 64, 128, 160 or 192 with it in tensor memory");
     if (plan->umma_sps != 0 && plan->umma_sps != 1 && plan->umma_sps != 2 && plan->umma_sps != 4)
         return fail(c, LUTAMM_EINVAL, "umma_sps must be 0, 1, 2 or 4");
-    if (plan->umma_mma_warps != 0 && plan->umma_mma_warps != 2 && plan->umma_mma_warps != 4)
-        return fail(c, LUTAMM_EINVAL, "umma_mma_warps must be 0, 2 or 4");
     if (plan->variant == LUTAMM_VARIANT_UMMA && !umma_supported(L->CB, L->CT, L->N))
         return fail(c, LUTAMM_EUNSUPPORTED, "tcgen05 variant does not cover this shape");
     L->plan = *plan;
@@ -823,6 +826,149 @@ int lutamm_get_timings(lutamm_ctx* c, lutamm_timings* out) {
     if (!out) return fail(c, LUTAMM_EINVAL, "null out pointer");
     if (!c->last_valid) return fail(c, LUTAMM_EINVAL, "no timed call yet (lutamm_enable_timing, then a synchronous call)");
     *out = c->last;
+    return LUTAMM_OK;
+}
+
+
+// ---- sharded forms -------------------------------------------------------------------------------
+int lutamm_shard_unique_id(char* id) {
+    if (!id) return fail(nullptr, LUTAMM_EINVAL, "null id buffer");
+    const NcclApi& n = nccl_api();
+    if (!n.ok) return fail(nullptr, LUTAMM_EUNSUPPORTED, n.why ? n.why : "NCCL unavailable");
+    NcclUniqueId u;
+    const int rc = n.get_unique_id(&u);
+    if (rc != kNcclSuccess) return fail(nullptr, LUTAMM_ECUDA, std::string("ncclGetUniqueId: ") + n.get_error_string(rc));
+    std::memcpy(id, u.internal, sizeof u.internal);
+    return LUTAMM_OK;
+}
+
+int lutamm_shard_init(lutamm_ctx* c, int rank, int world, const char* id) {
+    if (!c) return fail(nullptr, LUTAMM_EINVAL, "null context");
+    if (!id || world < 1 || rank < 0 || rank >= world) return fail(c, LUTAMM_EINVAL, "bad rank / world size / id");
+    const NcclApi& n = nccl_api();
+    if (!n.ok) return fail(c, LUTAMM_EUNSUPPORTED, n.why ? n.why : "NCCL unavailable");
+    DeviceGuard g(c->device);
+    if (c->comm) { n.comm_destroy(c->comm); c->comm = nullptr; }
+    NcclUniqueId u;
+    std::memcpy(u.internal, id, sizeof u.internal);
+    const int rc = n.comm_init_rank(&c->comm, world, u, rank);
+    if (rc != kNcclSuccess) { c->comm = nullptr; return fail(c, LUTAMM_ECUDA, std::string("ncclCommInitRank: ") + n.get_error_string(rc)); }
+    c->rank = rank;
+    c->world = world;
+    return LUTAMM_OK;
+}
+
+int lutamm_shard_finalize(lutamm_ctx* c) {
+    if (!c) return fail(nullptr, LUTAMM_EINVAL, "null context");
+    DeviceGuard g(c->device);
+    if (c->comm) {
+        CU_TRY(c, cudaStreamSynchronize(c->stream));
+        if (nccl_api().ok) nccl_api().comm_destroy(c->comm);
+        c->comm = nullptr;
+    }
+    c->rank = 0;
+    c->world = 1;
+    return LUTAMM_OK;
+}
+
+int lutamm_amm_column_sharded(lutamm_ctx* c, int layer_id, const float* input, float* gathered, uint32_t M,
+                              uint32_t search_mode, uint32_t flags) {
+    if (!c) return fail(nullptr, LUTAMM_EINVAL, "null context");
+    DeviceGuard g(c->device);
+    Layer* L = find_layer(c, layer_id);
+    if (!L) return fail(c, LUTAMM_ENOLAYER, "no weights loaded for layer " + std::to_string(layer_id));
+    if (M == 0) return LUTAMM_OK;
+    if (!input || !gathered) return fail(c, LUTAMM_EINVAL, "null input or output");
+    if (!is_device_ptr(input) || !is_device_ptr(gathered)) return fail(c, LUTAMM_EINVAL, "the sharded entry points take device buffers");
+    if (reinterpret_cast<uintptr_t>(gathered) & 15u) return fail(c, LUTAMM_EINVAL, "device output must be 16-byte aligned");
+    if (search_mode != LUTAMM_SHARD_SEARCH_REPLICATED && search_mode != LUTAMM_SHARD_SEARCH_SPLIT)
+        return fail(c, LUTAMM_EINVAL, "unknown search mode");
+    if (flags & LUTAMM_FLAG_OUTPUT_TILED) return fail(c, LUTAMM_EINVAL, "the gathered buffer already is the reference's tiled layout with lut_parallelism = world size");
+    const uint32_t G = (uint32_t)c->world, r = (uint32_t)c->rank;
+    if (G > 1 && !c->comm) return fail(c, LUTAMM_EINVAL, "lutamm_shard_init has not been called on this context");
+    const NcclApi& n = nccl_api();
+    int rc;
+    if ((rc = ensure(c, c->d_idx, (size_t)M * L->CB))) return rc;
+    uint8_t* d_idx = static_cast<uint8_t*>(c->d_idx.p);
+    if (search_mode == LUTAMM_SHARD_SEARCH_SPLIT && G > 1 && M % G == 0) {
+        // each rank searches its M / G tokens, the uint8 indices are all-gathered in place: M*CB bytes
+        // on the wire instead of G times the search
+        const uint32_t m_loc = M / G;
+        if ((rc = run_ccs(c, *L, input + (size_t)r * m_loc * L->K, d_idx + (size_t)r * m_loc * L->CB, m_loc, LUTAMM_INDEX_U8_ROWMAJOR))) return rc;
+        const int e = n.all_gather(d_idx + (size_t)r * m_loc * L->CB, d_idx, (size_t)m_loc * L->CB, kNcclUint8, c->comm, c->stream);
+        if (e != kNcclSuccess) return fail(c, LUTAMM_ECUDA, std::string("ncclAllGather(indices): ") + n.get_error_string(e));
+    } else {
+        if ((rc = run_ccs(c, *L, input, d_idx, M, LUTAMM_INDEX_U8_ROWMAJOR))) return rc;
+    }
+    // this rank's [M][N_loc] slab straight into block r of the gathered buffer, then the blocks in place
+    const size_t slab = (size_t)M * L->N;
+    if ((rc = run_lut(c, *L, d_idx, gathered + (size_t)r * slab, nullptr, M, 0, L->plan))) return rc;
+    if (G > 1) {
+        const int e = n.all_gather(gathered + (size_t)r * slab, gathered, slab, kNcclFloat32, c->comm, c->stream);
+        if (e != kNcclSuccess) return fail(c, LUTAMM_ECUDA, std::string("ncclAllGather(output slabs): ") + n.get_error_string(e));
+    }
+    if (flags & LUTAMM_FLAG_ASYNC) return LUTAMM_OK;
+    return check_dev_err(c);
+}
+
+int lutamm_amm_token_sharded(lutamm_ctx* c, int layer_id, const float* input_rows, float* output, uint32_t M_total,
+                             uint32_t gather, uint32_t flags) {
+    if (!c) return fail(nullptr, LUTAMM_EINVAL, "null context");
+    DeviceGuard g(c->device);
+    Layer* L = find_layer(c, layer_id);
+    if (!L) return fail(c, LUTAMM_ENOLAYER, "no weights loaded for layer " + std::to_string(layer_id));
+    if (M_total == 0) return LUTAMM_OK;
+    if (!input_rows || !output) return fail(c, LUTAMM_EINVAL, "null input or output");
+    if (!is_device_ptr(input_rows) || !is_device_ptr(output)) return fail(c, LUTAMM_EINVAL, "the sharded entry points take device buffers");
+    if (flags & LUTAMM_FLAG_OUTPUT_TILED) return fail(c, LUTAMM_EINVAL, "tiled output is not offered by the token-sharded call");
+    const uint32_t G = (uint32_t)c->world, r = (uint32_t)c->rank;
+    if (M_total % G) return fail(c, LUTAMM_EINVAL, "n_tokens must be a multiple of the world size");
+    if (G > 1 && gather && !c->comm) return fail(c, LUTAMM_EINVAL, "lutamm_shard_init has not been called on this context");
+    const uint32_t m_loc = M_total / G;
+    int rc;
+    if ((rc = ensure(c, c->d_idx, (size_t)m_loc * L->CB))) return rc;
+    float* mine = gather ? output + (size_t)r * m_loc * L->N : output;
+    if (reinterpret_cast<uintptr_t>(mine) & 15u) return fail(c, LUTAMM_EINVAL, "device output must be 16-byte aligned");
+    if ((rc = run_ccs(c, *L, input_rows, c->d_idx.p, m_loc, LUTAMM_INDEX_U8_ROWMAJOR))) return rc;
+    if ((rc = run_lut(c, *L, static_cast<const uint8_t*>(c->d_idx.p), mine, nullptr, m_loc, 0, L->plan))) return rc;
+    if (gather && G > 1) {
+        const NcclApi& n = nccl_api();
+        const int e = n.all_gather(mine, output, (size_t)m_loc * L->N, kNcclFloat32, c->comm, c->stream);
+        if (e != kNcclSuccess) return fail(c, LUTAMM_ECUDA, std::string("ncclAllGather(rows): ") + n.get_error_string(e));
+    }
+    if (flags & LUTAMM_FLAG_ASYNC) return LUTAMM_OK;
+    return check_dev_err(c);
+}
+
+int lutamm_measure_int8_peak(lutamm_ctx* c, double* tops, double* mac_per_clk_sm, double* sm_mhz) {
+    if (!c) return fail(nullptr, LUTAMM_EINVAL, "null context");
+    DeviceGuard g(c->device);
+    const uint32_t n_tile = 256, slabs = 8192, grid = (uint32_t)c->sm_count;
+    int r;
+    if ((r = ensure(c, c->d_build, 256))) return r;
+    unsigned long long* d_cycles = static_cast<unsigned long long*>(c->d_build.p);
+    const char* why = nullptr;
+    float best_ms = 1e30f;
+    unsigned long long cycles = 0;
+    for (int rep = 0; rep < 4; ++rep) {  // the first repetition warms up; the best of the rest counts
+        CU_TRY(c, cudaEventRecord(c->ev[0], c->stream));
+        cudaError_t e = launch_int8_peak(n_tile, slabs, grid, d_cycles, c->d_err, c->stream, &why);
+        if (e != cudaSuccess) return fail(c, LUTAMM_ECUDA, why ? why : (std::string("int8 peak launch: ") + cudaGetErrorString(e)));
+        ++c->launches;
+        CU_TRY(c, cudaEventRecord(c->ev[1], c->stream));
+        if ((r = check_dev_err(c))) return r;
+        float ms = 0;
+        CU_TRY(c, cudaEventElapsedTime(&ms, c->ev[0], c->ev[1]));
+        if (rep > 0 && ms < best_ms) {
+            best_ms = ms;
+            CU_TRY(c, cudaMemcpy(&cycles, d_cycles, sizeof cycles, cudaMemcpyDeviceToHost));
+        }
+    }
+    const double macs_per_cta = (double)slabs * 128.0 * n_tile * 128.0;
+    if (tops) *tops = 2.0 * macs_per_cta * grid / (best_ms * 1e-3) / 1e12;
+    if (mac_per_clk_sm) *mac_per_clk_sm = cycles ? macs_per_cta / (double)cycles : 0.0;
+    // event time covers launch and tear-down too, so this slightly understates the clock
+    if (sm_mhz) *sm_mhz = cycles ? (double)cycles / (best_ms * 1e-3) / 1e6 : 0.0;
     return LUTAMM_OK;
 }
 

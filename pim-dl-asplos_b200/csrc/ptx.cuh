@@ -49,19 +49,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// The same with an explicit suspend-time hint (nanoseconds): the thread may stay parked that long
-// before the instruction returns false, instead of the system-dependent default.
-__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t ns) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity), "r"(ns)
-        : "memory");
-    return ok != 0;
-}
 // Non-blocking probe of two barriers at once: true if both have completed the phase with their
 // parity.  A query takes a round trip of the order of a hundred cycles before its answer can be
 // used; issued back to back the two overlap, and a loop that needs the answer every turn asks one
@@ -89,16 +76,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (mbar_try_wait(bar, parity)) return true;
     if (*abort_word) return false;
     for (uint32_t it = 0; it < kWaitLimit; ++it) {
-#ifdef LUTAMM_WAIT_HINT_NS
-        if (mbar_try_wait_hint(bar, parity, LUTAMM_WAIT_HINT_NS)) return true;
-#else
         if (mbar_try_wait(bar, parity)) return true;
-#endif
         if ((it & 63u) == 63u && *abort_word) return false;
         if constexpr (kSleepNs > 0) __nanosleep(kSleepNs);
-#ifdef LUTAMM_EXP_SLEEP
-        else __nanosleep(LUTAMM_EXP_SLEEP);
-#endif
     }
     *abort_word = 1u;
     return false;

@@ -1,0 +1,68 @@
+"""One rank of the sharded-operator GPU test (launched by tests/test_shard_gpu.py through torchrun).
+
+Each rank: joins the library's own NCCL communicator, runs the column-sharded AMM (both search modes) and
+the token-sharded AMM (with and without the row all-gather) through the C ABI, and compares every result
+with the CPU oracle's unsharded output bit for bit.  NVLS is switched off by the launcher: the test only
+needs plain peer transfers.  Exit code 0 = every comparison held on this rank.
+"""
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+import oracle
+import pim_dl_asplos_b200 as P
+from pim_dl_asplos_b200 import shard, synth
+
+
+def main():
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    ctx = P.LutAmmContext(local)
+    ctx.shard_init()
+    M, K, N, v, CT = 512 * world, 256, 384 * world, 2, 16
+    c = synth.make_case(M=M, K=K, N=N, v=v, CT=CT, seed=3)
+    want = oracle.amm(c.x, c.centroid, c.lut, c.bias, c.scale, 0.0)[0]
+    x = torch.from_numpy(c.x).cuda()
+    n_loc = N // world
+    # ---- columns: this rank's slab of table and bias
+    lo, hi = shard.column_range(N, rank, world)
+    assert hi - lo == n_loc
+    ctx.load_weights(0, c.centroid, np.ascontiguousarray(c.lut[:, :, lo:hi]), np.ascontiguousarray(c.bias[lo:hi]), c.scale)
+    for plan in (dict(variant=P.VARIANT_AUTO), dict(variant=P.VARIANT_GATHER)):
+        ctx.set_plan(0, **plan)
+        for mode in (P.SHARD_SEARCH_REPLICATED, P.SHARD_SEARCH_SPLIT):
+            gathered = torch.full((world, M, n_loc), float("nan"), device="cuda")
+            ctx.amm_column_sharded(0, x, gathered, n_tokens=M, search_mode=mode)
+            got = gathered.permute(1, 0, 2).reshape(M, N).cpu().numpy()
+            assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), (rank, plan, mode, "column-sharded")
+            # the gathered buffer is the reference's tiled layout for lut_parallelism = world
+            offs = np.array([oracle.tiled_output_offset(i, j, M, n_loc, n_loc, world) for i in (0, M - 1) for j in (0, n_loc, N - 1)])
+            flat = gathered.reshape(-1).cpu().numpy()
+            ref = np.array([want[i, j] for i in (0, M - 1) for j in (0, n_loc, N - 1)])
+            assert np.array_equal(flat[offs].view(np.uint32), ref.view(np.uint32)), "not the reference's tiled layout"
+    ctx.unload_weights(0)
+    # ---- tokens: weights replicated
+    ctx.load_weights(1, c.centroid, c.lut, c.bias, c.scale)
+    m_lo, m_hi = shard.token_range(M, rank, world)
+    mine = torch.empty(m_hi - m_lo, N, device="cuda")
+    ctx.amm_token_sharded(1, x[m_lo:m_hi].contiguous(), mine, M, gather=False)
+    assert np.array_equal(mine.cpu().numpy().view(np.uint32), want[m_lo:m_hi].view(np.uint32)), (rank, "token-sharded")
+    full = torch.full((M, N), float("nan"), device="cuda")
+    ctx.amm_token_sharded(1, x[m_lo:m_hi].contiguous(), full, M, gather=True)
+    assert np.array_equal(full.cpu().numpy().view(np.uint32), want.view(np.uint32)), (rank, "token-sharded + gather")
+    ctx.shard_finalize()
+    ctx.close()
+    dist.barrier()
+    dist.destroy_process_group()
+    print(f"rank {rank}: sharded results bit-identical to the oracle")
+
+
+if __name__ == "__main__":
+    main()
