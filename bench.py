@@ -271,7 +271,16 @@ def run_ours(args):
     stream = torch.cuda.Stream()
     ctx.set_stream(stream.cuda_stream)
     if world > 1:
-        ctx.shard_init()   # the library's own NCCL communicator, for the sharded entry points
+        # the library's own NCCL communicator, for the sharded entry points; NCCL may print its version
+        # banner to stdout when a communicator is created: keep stdout to the one JSON line
+        sys.stdout.flush()
+        saved = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            ctx.shard_init()
+        finally:
+            os.dup2(saved, 1)
+            os.close(saved)
 
     layers = []
     for li, (name, K, N) in enumerate(w["linears"]):

@@ -273,6 +273,14 @@ int lutamm_set_activation(lutamm_ctx* ctx, int layer_id, uint32_t activation);
  * and installs the fastest.  best may be NULL. */
 int lutamm_tune(lutamm_ctx* ctx, int layer_id, uint32_t n_tokens, lutamm_plan* best);
 
+/* Plans found by lutamm_tune are remembered in the context by shape - (n_tokens, K, N, CB, CT, SM count) -
+ * and a later lutamm_tune for a shape it knows installs the remembered plan without measuring.  These two
+ * calls keep that table in a text file beside the configuration, so that a new process does not re-tune
+ * (the reference's tuner writes its result into the YAML, src/tuner/auto_tuner.cpp:552-603; so does the
+ * tuner here, and this file is the shape-keyed form of the same thing). */
+int lutamm_plan_cache_save(lutamm_ctx* ctx, const char* path);
+int lutamm_plan_cache_load(lutamm_ctx* ctx, const char* path);
+
 /* Turn per-stage CUDA-event timing on (non-zero) or off; the reference's AMM_BREAKDOWN
  * compile-time switch (amm_host.cpp:14-26, pim_lut_host.cpp:124-212) as a runtime flag. */
 int lutamm_enable_timing(lutamm_ctx* ctx, int on);
@@ -287,6 +295,14 @@ int lutamm_get_timings(lutamm_ctx* ctx, lutamm_timings* out);
  *   sm_mhz          the SM clock those two figures imply
  * Any pointer may be NULL. */
 int lutamm_measure_int8_peak(lutamm_ctx* ctx, double* tops, double* mac_per_clk_sm, double* sm_mhz);
+
+/* Self-test of the failure path every kernel of this library shares.  A one-CTA kernel sets up tensor
+ * memory and an mbarrier, then waits - with the library's bounded wait, cut to `polls` probes - for a barrier
+ * that nobody arrives at; the wait gives up, the kernel reports through the context's device error word, frees
+ * its tensor memory and returns.  The call therefore returns LUTAMM_EDEVICE, and the context must be fully
+ * usable afterwards (error word cleared, split-tile counters re-armed).  The reference has no counterpart: a
+ * DPU fault aborts its process (DPU_ASSERT, src/host/dpu_common.h:13). */
+int lutamm_selftest_bounded_wait(lutamm_ctx* ctx, uint32_t polls);
 
 /* Kernels of this library launched on this context since creation. */
 uint64_t lutamm_launch_count(const lutamm_ctx* ctx);

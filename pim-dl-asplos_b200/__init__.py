@@ -33,7 +33,8 @@ ABI_SYMBOLS = [
     "lutamm_amm_static_scratch", "lutamm_static_scratch_last_error", "lutamm_build_lut",
     "lutamm_load_weights_layout", "lutamm_measure_int8_peak",
     "lutamm_shard_unique_id", "lutamm_shard_init", "lutamm_shard_finalize", "lutamm_amm_column_sharded",
-    "lutamm_amm_token_sharded",
+    "lutamm_amm_token_sharded", "lutamm_plan_cache_save", "lutamm_plan_cache_load",
+    "lutamm_selftest_bounded_wait",
 ]
 SHARD_SEARCH_REPLICATED, SHARD_SEARCH_SPLIT = 0, 1
 SHARD_ID_BYTES = 128
@@ -125,6 +126,9 @@ def load_library() -> ctypes.CDLL:
     L.lutamm_shard_finalize.argtypes = [vp]
     L.lutamm_amm_column_sharded.argtypes = [vp, i32, vp, vp, u32, u32, u32]
     L.lutamm_amm_token_sharded.argtypes = [vp, i32, vp, vp, u32, u32, u32]
+    L.lutamm_selftest_bounded_wait.argtypes = [vp, u32]
+    L.lutamm_plan_cache_save.argtypes = [vp, ctypes.c_char_p]
+    L.lutamm_plan_cache_load.argtypes = [vp, ctypes.c_char_p]
     dp = ctypes.POINTER(ctypes.c_double)
     L.lutamm_measure_int8_peak.argtypes = [vp, dp, dp, dp]
     L.lutamm_launch_count.argtypes = [vp]
@@ -358,6 +362,13 @@ class LutAmmContext:
         tops, mac, mhz = ctypes.c_double(), ctypes.c_double(), ctypes.c_double()
         self._check(self._L.lutamm_measure_int8_peak(self._h, ctypes.byref(tops), ctypes.byref(mac), ctypes.byref(mhz)))
         return {"tops": tops.value, "mac_per_clk_sm": mac.value, "sm_mhz": mhz.value}
+
+    def plan_cache_save(self, path: str):
+        """Write the plans lutamm_tune has found in this context, keyed by shape and SM count, to a text file."""
+        self._check(self._L.lutamm_plan_cache_save(self._h, path.encode()))
+
+    def plan_cache_load(self, path: str):
+        self._check(self._L.lutamm_plan_cache_load(self._h, path.encode()))
 
     def enable_timing(self, on: bool = True):
         self._check(self._L.lutamm_enable_timing(self._h, 1 if on else 0))

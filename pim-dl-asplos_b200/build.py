@@ -17,6 +17,7 @@ LIB = os.path.join(HERE, "libpimdl_b200.so")
 HOST_LIB = os.path.join(HERE, "libpimdl_host.so")
 TEST_AMM = os.path.join(HERE, "bin", "test_amm")
 TUNER = os.path.join(HERE, "bin", "tuner")
+TEST_LAYER = os.path.join(HERE, "bin", "test_transformer_layer")
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-shared", "-cudart", "static"]
@@ -74,13 +75,13 @@ def build_host(force: bool = False) -> None:
     if not os.path.isdir(hdir):
         return
     os.makedirs(os.path.join(HERE, "bin"), exist_ok=True)
-    lib_srcs = [s for s in host_sources() if os.path.basename(s) not in ("test_amm.cpp", "auto_tuner.cpp")]
+    lib_srcs = [s for s in host_sources() if os.path.basename(s) not in ("test_amm.cpp", "auto_tuner.cpp", "test_transformer_layer.cpp")]
     deps = host_sources() + glob.glob(os.path.join(hdir, "*.h")) + [os.path.join(HERE, "..", "include", "lutamm.h")]
     common = ["g++", "-std=c++17", "-O2", "-Wall", "-fPIC", "-I", hdir, "-I", os.path.join(HERE, "..", "include")]
     rpath = ["-Wl,-rpath,$ORIGIN", "-Wl,-rpath,$ORIGIN/.."]
     if lib_srcs and (force or _stale(HOST_LIB, deps + [LIB])):
         subprocess.run(common + ["-shared", "-o", HOST_LIB] + lib_srcs + ["-L", HERE, "-lpimdl_b200"] + rpath, check=True)
-    for exe, src in ((TEST_AMM, "test_amm.cpp"), (TUNER, "auto_tuner.cpp")):
+    for exe, src in ((TEST_AMM, "test_amm.cpp"), (TUNER, "auto_tuner.cpp"), (TEST_LAYER, "test_transformer_layer.cpp")):
         sp = os.path.join(hdir, src)
         if os.path.exists(sp) and (force or _stale(exe, deps + [LIB])):
             subprocess.run(common + ["-o", exe, sp, "-L", HERE, "-lpimdl_host", "-lpimdl_b200", "-lpthread"] + rpath,

@@ -62,3 +62,32 @@ struct AMMParams {
     GpuPlan gpu_plan;    // all zero = library defaults
     uint32_t gpu_device; // system_params.gpu_device, default 0
 };
+
+// The encoder layer's parameter blocks, as in the reference (src/host/defines.h:58-95).
+struct AttentionParams {
+    uint32_t seq_len;
+    uint32_t batch_size;
+    uint32_t n;  // seq_len * batch_size
+    uint32_t head_num;
+    uint32_t head_dim;
+    uint32_t token_dim;
+    uint32_t dpu_num;            // UPMEM mapping of the QKV operator: carried, unused on the GPU
+    uint32_t input_parallelism;
+    uint32_t lut_parallelism;
+    uint32_t n_tile_size;
+    uint32_t token_tile_size;
+    uint32_t num_threads;
+};
+
+// amm_param_list: 0 QKV (token_dim -> 3 token_dim), 1 attention output, 2 FFN1, 3 FFN2 (ffn_hidden_dim ->
+// token_dim), 4-6 the separate Q / K / V operators (token_dim -> token_dim), which the reference fills from
+// the attention-output keys (src/host/parser.cpp:235-322).
+struct TransformerParams {
+    std::string pim_binary_list[4];  // *_lut_pim_binary: DPU kernel images, kept so a file round-trips
+    AMMParams amm_param_list[7];
+    AttentionParams attention_params;
+    uint32_t ffn_hidden_dim;
+    uint32_t layer_num;
+    uint32_t num_threads;
+    uint32_t gpu_device;
+};

@@ -84,4 +84,40 @@ cudaError_t launch_int8_peak(uint32_t n_tile, uint32_t slabs, uint32_t grid, uns
     return cudaGetLastError();
 }
 
+
+// ---- self-test of the way out after a wait that runs out -----------------------------------------
+// One CTA sets up what the tcgen05 LUT kernel sets up (tensor memory, an mbarrier), then one thread waits
+// - with the library's own bounded wait, limited to `polls` probes - on a barrier nobody ever arrives at.
+// The wait gives up, the abort word is set, the CTA goes through the same tear-down as the LUT kernel
+// (report in the device error word, everybody meets, tensor memory is freed) and returns.  Nothing traps and
+// nothing spins on: the host reads the error word and the context stays usable.
+namespace {
+__global__ void __launch_bounds__(128, 1) stalled_wait_kernel(uint32_t polls, uint32_t* dev_err) {
+    __shared__ uint32_t s_tmem;
+    __shared__ uint32_t s_abort;
+    __shared__ uint64_t s_bar;
+    if (threadIdx.x == 0) {
+        s_abort = 0;
+        mbar_init(smem_u32(&s_bar), 1);
+        fence_barrier_init();
+    }
+    __syncthreads();
+    if (threadIdx.x < 32) { tmem_alloc(smem_u32(&s_tmem), 32); tmem_relinquish(); }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    volatile uint32_t* abort_word = &s_abort;
+    if (threadIdx.x == 32) (void)mbar_wait_limited(smem_u32(&s_bar), 0, abort_word, polls);   // phase 0 never completes
+    __syncthreads();
+    if (*abort_word && threadIdx.x == 0) atomicExch(dev_err, 4u);
+    __syncthreads();
+    if (threadIdx.x < 32) { tc_fence_after_sync(); tmem_dealloc(s_tmem, 32); }
+}
+}  // namespace
+
+cudaError_t launch_stalled_wait(uint32_t polls, uint32_t* dev_err, cudaStream_t s) {
+    stalled_wait_kernel<<<1, 128, 0, s>>>(polls, dev_err);
+    return cudaGetLastError();
+}
+
 }  // namespace lutamm

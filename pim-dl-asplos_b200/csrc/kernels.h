@@ -95,6 +95,9 @@ cudaError_t launch_lut_untile(const int8_t* dpu, int8_t* canonical, uint32_t row
 cudaError_t launch_int8_peak(uint32_t n_tile, uint32_t slabs, uint32_t grid, unsigned long long* d_cycles, uint32_t* dev_err,
                              cudaStream_t s, const char** why);
 
+// Self-test: a bounded wait on a barrier nobody arrives at; the kernel reports through *dev_err and returns.
+cudaError_t launch_stalled_wait(uint32_t polls, uint32_t* dev_err, cudaStream_t s);
+
 // Driver entry point for tensor-map encoding, resolved through the runtime so the library
 // carries no link-time dependency on the driver and loads on machines without one.
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,

@@ -82,6 +82,8 @@ struct lutamm_ctx {
     bool last_valid = false;
     uint64_t launches = 0;
     std::string err;
+    // plans found by lutamm_tune, by shape: (n_tokens, K, N, CB, CT, SM count) -> plan
+    std::map<std::vector<uint32_t>, lutamm_plan> plan_cache;
     // sharding across the GPUs of a box (lutamm_shard_init)
     lutamm::NcclComm comm = nullptr;
     int rank = 0, world = 1;
@@ -268,7 +270,7 @@ int run_lut(lutamm_ctx* c, Layer& L, const uint8_t* d_idx, float* d_out, int32_t
     return LUTAMM_OK;
 }
 
-int run_ccs(lutamm_ctx* c, Layer& L, const float* d_x, void* d_idx, uint32_t M, uint32_t format) {
+int run_ccs(lutamm_ctx* c, Layer& L, const float* d_x, void* d_idx, uint32_t M, uint32_t format, int ccs_tokens = -1) {
     CcsArgs a{};
     a.x = d_x;
     a.centroid = L.d_centroid;
@@ -277,7 +279,7 @@ int run_ccs(lutamm_ctx* c, Layer& L, const float* d_x, void* d_idx, uint32_t M, 
     a.format = format;
     a.n_stile = L.ip.n_stile_size;
     a.cb_mtile = L.ip.cb_mtile_size;
-    a.tokens_per_thread = L.plan.ccs_tokens;
+    a.tokens_per_thread = ccs_tokens >= 0 ? (uint32_t)ccs_tokens : L.plan.ccs_tokens;
     const char* why = nullptr;
     cudaError_t e = launch_ccs(a, c->stream, &why);
     if (e != cudaSuccess) return fail(c, LUTAMM_ECUDA, why ? why : (std::string("search launch: ") + cudaGetErrorString(e)));
@@ -730,6 +732,14 @@ int lutamm_tune(lutamm_ctx* c, int layer_id, uint32_t M, lutamm_plan* best_out) 
     Layer* L = find_layer(c, layer_id);
     if (!L) return fail(c, LUTAMM_ENOLAYER, "no weights loaded for layer " + std::to_string(layer_id));
     if (M == 0) return fail(c, LUTAMM_EINVAL, "cannot tune for zero tokens");
+    // a shape tuned before on this kind of GPU (this process, or a cache file loaded into the context)
+    const std::vector<uint32_t> key = {M, L->K, L->N, L->CB, L->CT, (uint32_t)c->sm_count};
+    auto hit = c->plan_cache.find(key);
+    if (hit != c->plan_cache.end()) {
+        L->plan = hit->second;
+        if (best_out) *best_out = hit->second;
+        return LUTAMM_OK;
+    }
     int r;
     // Inputs: zero activations give valid indices; the kernels' timing does not depend on values.
     if ((r = ensure(c, c->d_in, (size_t)M * L->K * sizeof(float)))) return r;
@@ -737,6 +747,10 @@ int lutamm_tune(lutamm_ctx* c, int layer_id, uint32_t M, lutamm_plan* best_out) 
     if ((r = ensure(c, c->d_idx, (size_t)M * L->CB))) return r;
     CU_TRY(c, cudaMemsetAsync(c->d_in.p, 0, (size_t)M * L->K * sizeof(float), c->stream));
 
+    // The search space: kernel variant; for the CUDA-core gather its tile configuration; for tcgen05 where
+    // the one-hot operand lives, the tile width, the split of the codebook axis, the depth of the LUT ring
+    // and the number of one-hot builder groups.  (What the reference's tuner enumerates instead - DPU grid,
+    // micro-tile factors, load type, loop order, src/tuner/auto_tuner.cpp:368-549 - has no meaning here.)
     std::vector<lutamm_plan> cands;
     for (uint32_t cfg = 0; cfg < gather_num_cfgs(); ++cfg) {
         lutamm_plan p{};
@@ -747,13 +761,14 @@ int lutamm_tune(lutamm_ctx* c, int layer_id, uint32_t M, lutamm_plan* best_out) 
     if (umma_supported(L->CB, L->CT, L->N)) {
         const uint32_t slabs = (uint32_t)(((uint64_t)L->CB * L->CT + 127) / 128);
         struct Cand { uint32_t operand, n_tile, sps; };
-        for (const Cand& cd : {Cand{1, 256, 1}, Cand{2, 192, 1}, Cand{2, 128, 2}, Cand{2, 128, 1}, Cand{1, 128, 1}}) {
+        for (const Cand& cd : {Cand{1, 256, 1}, Cand{2, 192, 1}, Cand{2, 160, 1}, Cand{2, 128, 2}, Cand{2, 128, 1}, Cand{1, 128, 1}, Cand{2, 64, 1}}) {
             if (cd.n_tile > 128 && L->N < cd.n_tile) continue;
             const uint32_t tiles = ((M + 127) / 128) * ((L->N + cd.n_tile - 1) / cd.n_tile);
+            if (cd.n_tile == 64 && tiles > 4u * (uint32_t)c->sm_count) continue;  // narrow tiles only pay on small problems
             std::vector<uint32_t> splits = {1};
             uint32_t s_fill = tiles < (uint32_t)c->sm_count ? (uint32_t)c->sm_count / tiles : 1;
             for (uint32_t s : {s_fill, s_fill * 2, s_fill / 2})
-                if (s > 1 && s <= slabs / 4 && s <= 32) splits.push_back(s);
+                if (s > 1 && s <= slabs / 4 && s <= 32 && std::find(splits.begin(), splits.end(), s) == splits.end()) splits.push_back(s);
             for (uint32_t s : splits) {
                 lutamm_plan p{};
                 p.variant = LUTAMM_VARIANT_UMMA;
@@ -762,11 +777,19 @@ int lutamm_tune(lutamm_ctx* c, int layer_id, uint32_t M, lutamm_plan* best_out) 
                 p.umma_operand = cd.operand;
                 p.umma_sps = cd.sps;
                 cands.push_back(p);
+                if (s == 1 || s == s_fill) {  // ring depth and builder groups around the likely winners only
+                    lutamm_plan q = p;
+                    q.umma_stages = 6;
+                    cands.push_back(q);
+                    q = p;
+                    q.umma_groups = 2;
+                    cands.push_back(q);
+                }
             }
         }
     }
-    // ccs tokens-per-thread candidates are searched after the LUT variant
     cudaEvent_t e0 = c->ev[0], e1 = c->ev[1];
+    const std::string saved_err = c->err;
     auto time_lut = [&](const lutamm_plan& p, float* ms) -> int {
         int rr;
         for (int w = 0; w < 2; ++w)
@@ -783,25 +806,26 @@ int lutamm_tune(lutamm_ctx* c, int layer_id, uint32_t M, lutamm_plan* best_out) 
         return LUTAMM_OK;
     };
     if ((r = run_ccs(c, *L, static_cast<const float*>(c->d_in.p), c->d_idx.p, M, LUTAMM_INDEX_U8_ROWMAJOR))) return r;
+    // the layer's plan is replaced only when the whole search has succeeded
     lutamm_plan best = L->plan;
     float best_ms = 1e30f;
     for (const lutamm_plan& p : cands) {
         float ms = 0;
         r = time_lut(p, &ms);
         if (r == LUTAMM_EDEVICE) return r;
-        if (r) continue;  // a candidate the shape does not admit
+        if (r) { c->err = saved_err; continue; }  // a candidate the shape does not admit: not an error of the call
         if (ms < best_ms) { best_ms = ms; best = p; }
     }
+    if (best_ms >= 1e30f) return fail(c, LUTAMM_EUNSUPPORTED, "no kernel candidate could run this shape");
     // search granularity of step 1
     float best_ccs = 1e30f;
     uint32_t best_tok = 0;
-    for (uint32_t tok : {4u, 8u, 16u, 32u, 64u}) {
-        L->plan.ccs_tokens = tok;
+    for (uint32_t tok : {0u, 4u, 8u, 16u, 32u, 64u}) {
         for (int w = 0; w < 2; ++w)
-            if ((r = run_ccs(c, *L, static_cast<const float*>(c->d_in.p), c->d_idx.p, M, LUTAMM_INDEX_U8_ROWMAJOR))) return r;
+            if ((r = run_ccs(c, *L, static_cast<const float*>(c->d_in.p), c->d_idx.p, M, LUTAMM_INDEX_U8_ROWMAJOR, (int)tok))) return r;
         CU_TRY(c, cudaEventRecord(e0, c->stream));
         for (int i = 0; i < 5; ++i)
-            if ((r = run_ccs(c, *L, static_cast<const float*>(c->d_in.p), c->d_idx.p, M, LUTAMM_INDEX_U8_ROWMAJOR))) return r;
+            if ((r = run_ccs(c, *L, static_cast<const float*>(c->d_in.p), c->d_idx.p, M, LUTAMM_INDEX_U8_ROWMAJOR, (int)tok))) return r;
         CU_TRY(c, cudaEventRecord(e1, c->stream));
         CU_TRY(c, cudaStreamSynchronize(c->stream));
         float t = 0;
@@ -810,7 +834,50 @@ int lutamm_tune(lutamm_ctx* c, int layer_id, uint32_t M, lutamm_plan* best_out) 
     }
     best.ccs_tokens = best_tok;
     L->plan = best;
+    c->plan_cache[key] = best;
     if (best_out) *best_out = best;
+    return LUTAMM_OK;
+}
+
+// Plan cache as a text file: one line per shape, "n K N CB CT SMs : variant ccs_tokens gather_cfg n_tile split
+// stages groups operand sps".  A plan only applies to the GPU it was measured on, hence the SM count in the key.
+int lutamm_plan_cache_save(lutamm_ctx* c, const char* path) {
+    if (!c) return fail(nullptr, LUTAMM_EINVAL, "null context");
+    if (!path) return fail(c, LUTAMM_EINVAL, "null path");
+    FILE* f = std::fopen(path, "w");
+    if (!f) return fail(c, LUTAMM_EINVAL, std::string("cannot write ") + path);
+    std::fprintf(f, "# lutamm plan cache: n K N CB CT SMs : variant ccs_tokens gather_cfg n_tile split stages groups operand sps\n");
+    for (const auto& kv : c->plan_cache) {
+        const lutamm_plan& p = kv.second;
+        std::fprintf(f, "%u %u %u %u %u %u : %u %u %u %u %u %u %u %u %u\n", kv.first[0], kv.first[1], kv.first[2], kv.first[3], kv.first[4],
+                     kv.first[5], p.variant, p.ccs_tokens, p.gather_cfg, p.umma_n_tile, p.umma_split, p.umma_stages, p.umma_groups,
+                     p.umma_operand, p.umma_sps);
+    }
+    std::fclose(f);
+    return LUTAMM_OK;
+}
+
+int lutamm_plan_cache_load(lutamm_ctx* c, const char* path) {
+    if (!c) return fail(nullptr, LUTAMM_EINVAL, "null context");
+    if (!path) return fail(c, LUTAMM_EINVAL, "null path");
+    FILE* f = std::fopen(path, "r");
+    if (!f) return fail(c, LUTAMM_EINVAL, std::string("cannot read ") + path);
+    char line[512];
+    while (std::fgets(line, sizeof line, f)) {
+        if (line[0] == '#' || line[0] == '\n') continue;
+        unsigned k[6], v[9];
+        if (std::sscanf(line, "%u %u %u %u %u %u : %u %u %u %u %u %u %u %u %u", &k[0], &k[1], &k[2], &k[3], &k[4], &k[5], &v[0], &v[1], &v[2],
+                        &v[3], &v[4], &v[5], &v[6], &v[7], &v[8]) != 15) {
+            std::fclose(f);
+            return fail(c, LUTAMM_EINVAL, std::string("malformed plan cache line in ") + path);
+        }
+        lutamm_plan p{};
+        p.variant = v[0]; p.ccs_tokens = v[1]; p.gather_cfg = v[2]; p.umma_n_tile = v[3]; p.umma_split = v[4];
+        p.umma_stages = v[5]; p.umma_groups = v[6]; p.umma_operand = v[7]; p.umma_sps = v[8];
+        if (p.variant > LUTAMM_VARIANT_UMMA || p.gather_cfg >= gather_num_cfgs() || p.umma_operand > 2) continue;  // not a plan of this build
+        c->plan_cache[{k[0], k[1], k[2], k[3], k[4], k[5]}] = p;
+    }
+    std::fclose(f);
     return LUTAMM_OK;
 }
 
@@ -970,6 +1037,16 @@ int lutamm_measure_int8_peak(lutamm_ctx* c, double* tops, double* mac_per_clk_sm
     // event time covers launch and tear-down too, so this slightly understates the clock
     if (sm_mhz) *sm_mhz = cycles ? (double)cycles / (best_ms * 1e-3) / 1e6 : 0.0;
     return LUTAMM_OK;
+}
+
+int lutamm_selftest_bounded_wait(lutamm_ctx* c, uint32_t polls) {
+    if (!c) return fail(nullptr, LUTAMM_EINVAL, "null context");
+    DeviceGuard g(c->device);
+    if (polls == 0 || polls > (1u << 20)) return fail(c, LUTAMM_EINVAL, "polls must be in 1 .. 2^20");
+    cudaError_t e = launch_stalled_wait(polls, c->d_err, c->stream);
+    if (e != cudaSuccess) return fail(c, LUTAMM_ECUDA, std::string("self-test launch: ") + cudaGetErrorString(e));
+    ++c->launches;
+    return check_dev_err(c);   // LUTAMM_EDEVICE is the expected answer
 }
 
 uint64_t lutamm_launch_count(const lutamm_ctx* c) { return c ? c->launches : 0; }

@@ -72,16 +72,20 @@ __device__ __forceinline__ bool mbar_test2(uint32_t b0, uint32_t p0, uint32_t b1
 // waiting out a whole main loop, a producer waiting for a free stage): their polling otherwise
 // competes for issue slots and for the shared-memory pipe with the warps on the critical path.
 template <uint32_t kSleepNs = 0>
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_word) {
+__device__ __forceinline__ bool mbar_wait_limited(uint32_t bar, uint32_t parity, volatile uint32_t* abort_word, uint32_t limit) {
     if (mbar_try_wait(bar, parity)) return true;
     if (*abort_word) return false;
-    for (uint32_t it = 0; it < kWaitLimit; ++it) {
+    for (uint32_t it = 0; it < limit; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((it & 63u) == 63u && *abort_word) return false;
         if constexpr (kSleepNs > 0) __nanosleep(kSleepNs);
     }
     *abort_word = 1u;
     return false;
+}
+template <uint32_t kSleepNs = 0>
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_word) {
+    return mbar_wait_limited<kSleepNs>(bar, parity, abort_word, kWaitLimit);
 }
 
 // generic-proxy writes to shared memory -> visible to the async proxy (TMA, tcgen05.mma)

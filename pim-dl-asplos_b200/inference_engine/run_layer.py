@@ -34,6 +34,9 @@ def parse_args():
     p.add_argument('--tune', action='store_true', default=False)
     p.add_argument('--model_weight_file', type=str, default=None)
     p.add_argument('--layers', type=int, default=None, help='override layer_num (run_layer: 1)')
+    p.add_argument('--separate_qkv', action='store_true', default=False,
+                   help='run Q, K and V as three operators (the reference model driver\'s SEPARATE build, run_model.py:130); '
+                        'a checkpoint that holds query/key/value instead of a fused qkv operator selects this by itself')
     p.add_argument('--separate_gelu', action='store_true', default=False,
                    help='run GELU as its own pass after FFN1, as the reference does, instead of in the FFN1 epilogue')
     return p.parse_args()
@@ -66,20 +69,26 @@ def run(args, whole_model: bool):
     elif args.model_weight_file:
         print("weight file not found, using random weights (as test_transformer.cpp:484-489 does)")
     weights = []
+    if npz is not None:
+        n_layers = min(n_layers, L.checkpoint_layer_count(npz)) or n_layers
     for li in range(n_layers):
         if npz is not None:
-            weights.append(L.load_layer_weights_npz(npz, li, D, F, cfg["num_codebook"], cfg["num_centroid"]))
+            weights.append(L.load_layer_weights_npz(npz, li, D, F, cfg["num_codebook"], cfg["num_centroid"],
+                                                    separate_qkv=True if args.separate_qkv else None))
         else:
-            w = L.random_layer_weights(D, F, cfg["num_codebook"], cfg["num_centroid"], seed=0, layer=li)
-            for name in L.LINEARS:
+            w = L.random_layer_weights(D, F, cfg["num_codebook"], cfg["num_centroid"], seed=0, layer=li,
+                                       separate_qkv=args.separate_qkv)
+            for name in (L.SEPARATE_LINEARS if args.separate_qkv else L.LINEARS):
                 cen, lut, bias, _, _ = w[name]
-                w[name] = (cen, lut, bias, cfg["scale"][name], cfg["lut_bias"][name])
+                key = name if name in cfg["scale"] else "o"
+                w[name] = (cen, lut, bias, cfg["scale"][key], cfg["lut_bias"][key])
             weights.append(w)
+    print("attention projections:", "separate Q / K / V operators" if "qkv" not in weights[0] else "one fused QKV operator")
     model = L.LutTransformer(ctx, weights, S, B, H, plans=cfg["plans"], fused_gelu=not getattr(args, "separate_gelu", False))
     if args.tune:
         plans = model.layers[0].tune()
         for lay in model.layers[1:]:
-            for name in L.LINEARS:
+            for name in lay.linears:
                 ctx.set_plan(lay.ids[name], **plans[name])
         out = os.path.splitext(args.transformer_config_file)[0] + ".tuned.yaml"
         transformer_config.save_with_plans(raw, plans, out)
@@ -108,11 +117,12 @@ def run(args, whole_model: bool):
 
     if args.need_breakdown:
         ctx.enable_timing(True)
-        names = {"qkv": "qkv projection", "o": "o projection", "ffn1": "ffn1", "ffn2": "ffn2"}
+        names = {"qkv": "qkv projection", "q": "q projection", "k": "k projection", "v": "v projection",
+                 "o": "o projection", "ffn1": "ffn1", "ffn2": "ffn2"}
         lay = model.layers[0]
-        inputs = {"qkv": x, "o": x, "ffn1": x, "ffn2": torch.zeros(n, F, device="cuda")}
+        inputs = {"qkv": x, "q": x, "k": x, "v": x, "o": x, "ffn1": x, "ffn2": torch.zeros(n, F, device="cuda")}
         amm_total = 0.0
-        for name in L.LINEARS:
+        for name in lay.linears:
             ctx.amm_host(lay.ids[name], inputs[name], lay.buf[name], n_tokens=n)
             t = ctx.timings()
             amm_total += t["total_ms"]

@@ -29,6 +29,10 @@ def load(path):
         plan = {k: int(ker[f"{name}_gpu_{k}"]) for k in PLAN_KEYS if f"{name}_gpu_{k}" in ker}
         if plan:
             cfg["plans"][name] = plan
+    for name in ("q", "k", "v"):   # separate projections: shapes from the attention-output keys (parser.cpp:235-322), own plans if tuned
+        plan = {k: int(ker[f"{name}_gpu_{k}"]) for k in PLAN_KEYS if f"{name}_gpu_{k}" in ker}
+        if plan:
+            cfg["plans"][name] = plan
     return cfg, y
 
 

@@ -138,3 +138,81 @@ def test_sensitivity_sweep_configs(tmp_path):
         cfg, _ = transformer_config.load(str(tmp_path / "configs" / f))
         assert cfg["token_dim"] % cfg["num_codebook"]["qkv"] == 0
     assert rx.reference_cpu_seconds("batch-size", "bert-large", 32) == 2.32561
+
+
+LAYER = textwrap.dedent("""\
+    network_params:
+      seq_len: 64
+      batch_size: 8
+      head_num: 4
+      head_dim: 64
+      token_dim: 256
+      ffn_hidden_dim: 1024
+      layer_num: 3
+
+    system_params:
+      dpu_num: 64
+      nr_tasklets: 16
+      qkv_lut_pim_binary: "./build/bin/dpu_bin_qkv"
+      o_lut_pim_binary: "./build/bin/dpu_bin_o"
+      ffn1_lut_pim_binary: "./build/bin/dpu_bin_ffn1"
+      ffn2_lut_pim_binary: "./build/bin/dpu_bin_ffn2"
+      num_threads: 40
+
+    kernel_params:
+    """) + "".join(textwrap.indent(textwrap.dedent(f"""\
+      {p}_scale: 0.1
+      {p}_bias: 0.2
+      {p}_num_codebook: {cb}
+      {p}_num_centroid: 16
+      {p}_input_parallelism: 8
+      {p}_lut_parallelism: 8
+      {p}_loop_order: 0
+      {p}_lut_load_type: 2
+      {p}_n_mtile_size: 32
+      {p}_feature_mtile_size: 32
+      {p}_cb_mtile_size: 32
+      {p}_feature_load_tile_size: 8
+      {p}_cb_load_tile_size: 32
+    """), "  ") for p, cb in (("qkv", 64), ("o", 64), ("ffn1", 64), ("ffn2", 256)))
+
+
+def test_cpp_transformer_parser_reads_the_reference_schema(tmp_path):
+    """parse_transformer_configs (src/host/parser.cpp:89-413) in C++, through the layer driver: the reference's
+    full schema incl. the UPMEM mapping keys, derived values, and FFN2 as ffn_hidden_dim -> token_dim."""
+    cfg = tmp_path / "layer.yaml"
+    cfg.write_text(LAYER)
+    r = run("test_transformer_layer", str(cfg))
+    assert "layer num 3" in r.stdout and "thread num 40" in r.stdout
+    assert "n 512, input feature len 256, output feature len 768" in r.stdout        # QKV: 3 x token_dim
+    assert "n 512, input feature len 1024, output feature len 256" in r.stdout       # FFN2
+    assert "num codebook 256, num centroid 16, sub vec len 4" in r.stdout
+    assert "scale 0.1, bias 0.2" in r.stdout
+    assert "head num 4, head dim 64, token dim 256" in r.stdout
+    if not torch.cuda.is_available():
+        assert r.returncode == 1 and "cannot create a GPU context" in r.stderr
+
+
+@pytest.mark.parametrize("edit,msg", [
+    (("ffn2_num_codebook: 256", "ffn2_num_codebook: 100"), "ffn2: input feature length is not a multiple of num_codebook"),
+    (("head_dim: 64", "head_dim: 48"), "head_dim * head_num != token_dim"),
+    (("  o_input_parallelism: 8", "  o_input_parallelism: 16"), "o: input_parallelism * lut_parallelism != dpu_num"),
+    (("  ffn1_cb_load_tile_size: 32", "  ffn1_cb_load_tile_size: 5"), "ffn1: cb_mtile_size % cb_load_tile_size"),
+    (("  qkv_num_centroid: 16\n", ""), "missing kernel_params.qkv_num_centroid"),
+    (("  seq_len: 64\n", ""), "missing network_params.seq_len"),
+])
+def test_cpp_transformer_parser_rejects_bad_configs(tmp_path, edit, msg):
+    cfg = tmp_path / "bad.yaml"
+    assert edit[0] in LAYER
+    cfg.write_text(LAYER.replace(*edit))
+    r = run("test_transformer_layer", str(cfg))
+    assert r.returncode == 2, r.stdout + r.stderr
+    assert msg in r.stderr
+
+
+def test_cpp_transformer_parser_accepts_the_shipped_configs():
+    for name, want in (("bert_base_layer.yaml", "n 1024, input feature len 3072, output feature len 768"),
+                       ("bert_large_layer.yaml", "n 8192, input feature len 4096, output feature len 1024"),
+                       ("vit_base_model.yaml", "layer num 12")):
+        r = run("test_transformer_layer", os.path.join(CFG, name))
+        assert want in r.stdout, r.stdout + r.stderr
