@@ -47,7 +47,9 @@ _LIB_PATH = os.path.join(_HERE, "liblutamm_oracle.so")
 _REF_PATH = os.path.join(_HERE, "_ref", "libref_index_calc.so")
 _REF_AMM_PATH = os.path.join(_HERE, "_ref", "libref_amm_host.so")
 _REF_AMM_CPU_PATH = os.path.join(_HERE, "_ref", "libref_amm_cpu.so")
-_REF_TREE = os.environ.get("LUTAMM_REFERENCE_DIR", "/root/reference")
+# The reference tree (needed only to rebuild oracle/_ref): $LUTAMM_REFERENCE_DIR, else a checkout named
+# `reference` beside this repository.
+_REF_TREE = os.environ.get("LUTAMM_REFERENCE_DIR") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
 
 _u32 = ctypes.c_uint32
 _fp = ctypes.POINTER(ctypes.c_float)

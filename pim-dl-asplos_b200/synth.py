@@ -71,7 +71,7 @@ def make_case(M: int, K: int, N: int, v: int, CT: int, seed=0, scale: float = 0.
     return AmmCase(x, centroid, lut, bias, float(np.float32(scale)), float(np.float32(lut_bias)))
 
 
-# BASELINE shapes ------------------------------------------------------------------------
+# benchmark workloads ---------------------------------------------------------------------
 # name -> (M, [(linear name, K, N)], v, CT)
 BERT_BASE = [("qkv", 768, 2304), ("o", 768, 768), ("ffn1", 768, 3072), ("ffn2", 3072, 768)]
 BERT_LARGE = [("qkv", 1024, 3072), ("o", 1024, 1024), ("ffn1", 1024, 4096), ("ffn2", 4096, 1024)]

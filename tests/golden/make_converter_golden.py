@@ -18,7 +18,8 @@ import tempfile
 import numpy as np
 
 OUT = os.path.dirname(os.path.abspath(__file__))
-REF = os.environ.get("LUTAMM_REFERENCE_DIR", "/root/reference")
+# the reference tree: $LUTAMM_REFERENCE_DIR, else a checkout named `reference` beside this repository
+REF = os.environ.get("LUTAMM_REFERENCE_DIR") or os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(OUT))), "reference")
 
 FEATURES, VEC_LEN, NCENT = 32, 2, 16
 LINEARS = {  # name -> (in_features, out_features), pim_weight_converter.py:72-79

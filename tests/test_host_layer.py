@@ -216,3 +216,15 @@ def test_cpp_transformer_parser_accepts_the_shipped_configs():
                        ("vit_base_model.yaml", "layer num 12")):
         r = run("test_transformer_layer", os.path.join(CFG, name))
         assert want in r.stdout, r.stdout + r.stderr
+
+
+def test_search_space_sweep_points():
+    """The plan-space sweep that stands for asplos24-ae/search-space-illustration: every exploration lists its
+    points without a GPU, the global table is the union without duplicates."""
+    sys.path.insert(0, os.path.join(PKG, "inference_engine"))
+    import search_space as ss
+    pts = ss.main(["--dry_run"])
+    assert set(pts) == set(ss.EXPERIMENTS)
+    assert "2-192" in pts["operand-tile"] and "1-256" in pts["operand-tile"] and len(pts["gather"]) == 5
+    assert len(pts["global"]) == len(set(pts["global"])) >= 25
+    assert ss.SHAPE == dict(n=32768, K=1024, N=4096, CB=256, CT=16)

@@ -198,3 +198,16 @@ def test_tuner_mode_1_and_the_cpp_layer_driver(tmp_path):
     r = subprocess.run([sys.executable, os.path.join(PKG, "inference_engine", "run_layer.py"), "--transformer_config_file", str(out)],
                        capture_output=True, text=True, timeout=600)
     assert r.returncode == 0 and "AVG inference time" in r.stdout, r.stdout[-1500:] + r.stderr[-1500:]
+
+
+def test_search_space_sweep_single_point_and_experiment(tmp_path):
+    eng = os.path.join(PKG, "inference_engine")
+    r = subprocess.run([sys.executable, os.path.join(eng, "search_space.py"), "--single_point", "--experiment_type", "operand-tile",
+                        "--exploration_value", "2-192", "--tokens", "4096"], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "PIM AVG AMM time" in r.stdout, r.stdout[-1500:] + r.stderr[-1500:]
+    sys.path.insert(0, eng)
+    import search_space as ss
+    bench = ss.Bench(4096, 0)
+    rows = ss.run_experiment(bench, "gather", str(tmp_path))
+    bench.ctx.close()
+    assert len(rows) == 5 and all(r["amm_time_s"] > 0 for r in rows) and (tmp_path / "gather.csv").exists()

@@ -63,7 +63,7 @@ def test_golden_vectors(ctx, name):
 
 
 def test_config1_bert_base_ffn1(ctx):
-    """BASELINE config 1: M=512, K=768, N=3072, v=2, CT=16, seed 0."""
+    """Workload c1, the single BERT-base FFN1 linear: M=512, K=768, N=3072, v=2, CT=16, seed 0."""
     c = synth.make_case(M=512, K=768, N=3072, v=2, CT=16, seed=0)
     check_case(ctx, c.x, c.centroid, c.lut, c.bias, c.scale, c.lut_bias)
 
@@ -374,7 +374,7 @@ def test_tuner_installs_a_working_plan(ctx):
 
 
 def test_large_shape_properties(ctx):
-    """BASELINE config 5 is too large for a full CPU check on every run (2.2e12 byte adds),
+    """Workload c5 (65536 tokens, 4096 -> 16384) is too large for a full CPU check on every run (2.2e12 byte adds),
     so at that size: (1) a strided subsample of tokens is compared with the oracle - tokens
     are independent, so any row is checked as a whole; (2) every output row is checked
     through a checksum that does not depend on the size: sum_n acc[m][n] equals the gather
