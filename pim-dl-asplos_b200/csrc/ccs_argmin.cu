@@ -86,7 +86,7 @@ ccs_reg_kernel(const float* __restrict__ x, const float* __restrict__ cent, void
 #pragma unroll
     for (int t = 0; t < kTok; ++t) load_x<V>(xp + (size_t)min(m0 + t, M - 1) * K, xs[t]);
 
-    // Centroids are kept negated so that x - c becomes x + (-c): the same IEEE result, and
+    // Centroids are kept negated (the sign is flipped while they are staged) so that x - c becomes x + (-c): the same IEEE result, and
     // for even V two dimensions go through one packed add.rn.f32x2 / mul.rn.f32x2 (each lane
     // of a packed operation rounds on its own, and add and mul stay separate instructions,
     // so this is still the reference's unfused arithmetic).
@@ -95,23 +95,35 @@ ccs_reg_kernel(const float* __restrict__ x, const float* __restrict__ cent, void
     // per-thread reads below are bank-conflict free), instead of every lane walking its own
     // 128-byte stretch of global memory.
     constexpr int kRow = CT * V;
-    __shared__ float s_cent[kRegThreads * (kRow + 1)];
+    // With more than 32 centroid floats per codebook the negated centroids stay in shared memory and
+    // are read per centroid as 16-byte (V % 4 == 0) or 8-byte loads shared by the kTok tokens in flight:
+    // held in registers they cost CT*V registers per thread (126 in all at V = 4, CT = 16: four CTAs per
+    // SM, a fifth of the warps the SM can hold).  The row pitch keeps the loads aligned and conflict free
+    // (kRow + 4 words for 16-byte loads: the eight threads of a quarter warp land in eight different
+    // four-bank groups; kRow + 2 for 8-byte loads: the sixteen threads of a half warp in sixteen pairs).
+    constexpr int kVec = (V % 4 == 0) ? 4 : 2;   // floats per shared-memory load of a centroid
+    constexpr bool kCentInSmem = (V % 2 == 0) && (kRow >= 64 || (V >= 4 && kRow >= 32));
+    constexpr int kPitch = kCentInSmem ? kRow + kVec : kRow + 1;
+    __shared__ __align__(16) float s_cent[kRegThreads * kPitch];
     {
         const uint32_t cb0 = blockIdx.x * kRegThreads;
         const uint32_t n_cb = min((uint32_t)kRegThreads, CB - cb0);
         const float* gp = cent + (size_t)cb0 * kRow;
         for (uint32_t e = threadIdx.x; e < n_cb * kRow; e += kRegThreads) {
             const uint32_t r = e / kRow, i = e % kRow;
-            s_cent[r * (kRow + 1) + i] = __ldg(gp + e);
+            s_cent[r * kPitch + i] = -__ldg(gp + e);
         }
     }
     __syncthreads();
     if (!active) return;
-    float nc[CT][V];
+    float nc[kCentInSmem ? 1 : CT][V];
+    const float* my_cent = s_cent + threadIdx.x * kPitch;
+    if constexpr (!kCentInSmem) {
 #pragma unroll
-    for (int ct = 0; ct < CT; ++ct)
+        for (int ct = 0; ct < CT; ++ct)
 #pragma unroll
-        for (int d = 0; d < V; ++d) nc[ct][d] = -s_cent[threadIdx.x * (kRow + 1) + ct * V + d];
+            for (int d = 0; d < V; ++d) nc[ct][d] = my_cent[ct * V + d];
+    }
 
     for (uint32_t m = m0; m < m1; m += kTok) {
         float cur[kTok][V];
@@ -127,13 +139,32 @@ ccs_reg_kernel(const float* __restrict__ x, const float* __restrict__ cent, void
         uint32_t best[kTok];
 #pragma unroll
         for (int ct = 0; ct < CT; ++ct) {
+            float ncv[V];   // this centroid, negated
+            if constexpr (kCentInSmem) {
+                if constexpr (kVec == 4) {
+#pragma unroll
+                    for (int q = 0; q < V / 4; ++q) {
+                        const float4 c4 = *reinterpret_cast<const float4*>(my_cent + ct * V + 4 * q);
+                        ncv[4 * q + 0] = c4.x; ncv[4 * q + 1] = c4.y; ncv[4 * q + 2] = c4.z; ncv[4 * q + 3] = c4.w;
+                    }
+                } else {
+#pragma unroll
+                    for (int q = 0; q < V / 2; ++q) {
+                        const float2 c2 = *reinterpret_cast<const float2*>(my_cent + ct * V + 2 * q);
+                        ncv[2 * q + 0] = c2.x; ncv[2 * q + 1] = c2.y;
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int d = 0; d < V; ++d) ncv[d] = nc[ct][d];
+            }
 #pragma unroll
             for (int t = 0; t < kTok; ++t) {
                 float acc = 0.f;
                 if constexpr (V % 2 == 0) {
 #pragma unroll
                     for (int d = 0; d < V; d += 2) {
-                        const float2 e = __fadd2_rn(make_float2(cur[t][d], cur[t][d + 1]), make_float2(nc[ct][d], nc[ct][d + 1]));
+                        const float2 e = __fadd2_rn(make_float2(cur[t][d], cur[t][d + 1]), make_float2(ncv[d], ncv[d + 1]));
                         const float2 sq = __fmul2_rn(e, e);
                         acc = (d == 0) ? sq.x : __fadd_rn(acc, sq.x);  // 0 + sq.x is exact
                         acc = __fadd_rn(acc, sq.y);
@@ -141,7 +172,7 @@ ccs_reg_kernel(const float* __restrict__ x, const float* __restrict__ cent, void
                 } else {
 #pragma unroll
                     for (int d = 0; d < V; ++d) {
-                        const float e = __fadd_rn(cur[t][d], nc[ct][d]);
+                        const float e = __fadd_rn(cur[t][d], ncv[d]);
                         acc = __fadd_rn(acc, __fmul_rn(e, e));
                     }
                 }
@@ -266,15 +297,30 @@ cudaError_t launch_dependent(void (*k)(KArgs...), dim3 grid, dim3 block, size_t 
 
 template <int V, int CT, int kTok>
 cudaError_t run_reg_tok(const CcsArgs& a, cudaStream_t s) {
-    // Default run length per thread: long enough to amortise the centroid load, short enough
-    // that a small batch still spreads over the whole GPU (about 8 CTAs of 4 warps per SM).
+    // Run length per thread.  The grid is sized in whole waves of what the GPU holds at once - SMs x CTAs
+    // resident per SM for this instance (registers and shared memory decide: 6 to 8) - because a last wave
+    // that is a third full costs as much as a full one: a small batch is spread over as many CTAs as it has
+    // 4-token runs (one partial wave), a large one gets runs of up to 128 tokens, which also amortise the
+    // centroid staging, in an integral number of nearly full waves.
     uint32_t tpt = a.tokens_per_thread;
     if (!tpt) {
+        static int resident = 0, sms = 0;   // per instance; the same for every device of one kind
+        if (!resident) {
+            int dev = 0, r = 0;
+            cudaGetDevice(&dev);
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&r, ccs_reg_kernel<V, CT, false, kTok>, kRegThreads, 0) != cudaSuccess || r < 1) r = 4;
+            if (sms < 1) sms = 148;
+            resident = r;
+        }
         const uint64_t cb_blocks = (a.CB + kRegThreads - 1) / kRegThreads;
-        const uint64_t want_ctas = 148ull * 8ull;
-        tpt = (uint32_t)((a.M * cb_blocks + want_ctas - 1) / want_ctas);
+        const uint64_t wave = (uint64_t)sms * resident;
+        constexpr uint64_t kCap = 128;
+        const uint64_t ctas_at_cap = cb_blocks * ((a.M + kCap - 1) / kCap);
+        const uint64_t waves = ctas_at_cap <= wave ? 1 : (ctas_at_cap + wave - 1) / wave;
+        tpt = (uint32_t)(((uint64_t)a.M * cb_blocks + waves * wave - 1) / (waves * wave));
         if (tpt < (uint32_t)kTok) tpt = kTok;
-        if (tpt > 64u) tpt = 64u;
+        if (tpt > kCap) tpt = kCap;
     }
     tpt = (tpt + kTok - 1) / kTok * kTok;
     dim3 grid((a.CB + kRegThreads - 1) / kRegThreads, (a.M + tpt - 1) / tpt);
