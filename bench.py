@@ -736,6 +736,16 @@ def leg_c5_sharded(ctx, stream, m_total, rank, world, P, synth, torch, dist, ora
         res[name] = timed(lambda: ctx.amm_column_sharded(911, x, y_all, n_tokens=m_total, search_mode=mode, flags=P.FLAG_ASYNC))
     got = y_all[:, torch.from_numpy(rows).cuda(), :].permute(1, 0, 2).reshape(len(rows), N).cpu().numpy()
     ok = bool(np.array_equal(got.view(np.uint32), want.view(np.uint32)))
+    # the exchange fused into the kernel's epilogue (peer stores over NVLink instead of the all-gather)
+    fused_ms, fused_ok = None, None
+    if world > 1:
+        y_peer = ctx.shard_alloc_gathered(world, m_total, n_loc)
+        fused_ms = timed(lambda: ctx.amm_column_sharded(911, x, y_peer, n_tokens=m_total, search_mode=P.SHARD_SEARCH_SPLIT,
+                                                        flags=P.FLAG_ASYNC | P.FLAG_PEER_STORE))
+        gotp = y_peer[:, torch.from_numpy(rows).cuda(), :].permute(1, 0, 2).reshape(len(rows), N).cpu().numpy()
+        fused_ok = all_ok(bool(np.array_equal(gotp.view(np.uint32), want.view(np.uint32))))
+        barrier()
+        ctx.shard_free_gathered(y_peer)
     # the parts: this rank's kernels alone (world-size-1 call on its slab), the all-gather alone, and the optional
     # re-layout to row-major [M][N] for callers that do not take the reference's slab-major layout
     kern = timed(lambda: ctx.amm_host(911, x, y_all[rank], n_tokens=m_total, flags=P.FLAG_ASYNC))
@@ -751,11 +761,16 @@ def leg_c5_sharded(ctx, stream, m_total, rank, world, P, synth, torch, dist, ora
         with torch.cuda.stream(stream):
             y_full.view(m_total, world, n_loc).copy_(y_all.permute(1, 0, 2))
     rel = timed(relayout)
+    if fused_ms is not None:
+        res["fused_peer_stores"] = fused_ms
     best = min(res.values())
     gathered_bytes = (world - 1) * m_total * n_loc * 4      # received per rank
     out["n"] = {"ms": best, "tokens_per_s": m_total / (best * 1e-3), "ms_by_search_mode": res, "kernels_ms": kern, "collective_ms": coll,
                 "relayout_ms": rel, "tokens_per_s_with_relayout": m_total / ((best + rel) * 1e-3),
-                "allgather_gbs_per_rank": gathered_bytes / (coll * 1e-3) / 1e9 if coll else None, "parity_ok": all_ok(ok),
+                "allgather_gbs_per_rank": gathered_bytes / (coll * 1e-3) / 1e9 if coll else None,
+                "fused_peer_stores_ms": fused_ms, "fused_parity_ok": fused_ok,
+                "fused_nvlink_gbs_per_rank": gathered_bytes / (fused_ms * 1e-3) / 1e9 if fused_ms else None,
+                "parity_ok": all_ok(ok) and (fused_ok is not False),
                 "what": "columns split, all tokens on every rank, slabs all-gathered in place into [G][M][N/G] "
                         "(the reference's tiled output for lut_parallelism = G); relayout = optional copy to row-major"}
     ctx.unload_weights(911)

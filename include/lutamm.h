@@ -42,6 +42,8 @@ extern "C" {
 #define LUTAMM_FLAG_ASYNC         1u  /* return without waiting; input and output both device memory, or both
                                          host memory (pinned, for real overlap) that stays valid and untouched
                                          until lutamm_sync() */
+#define LUTAMM_FLAG_PEER_STORE    4u  /* lutamm_amm_column_sharded only: the kernel stores this rank's slab into
+                                         every rank's gathered buffer itself (see below) instead of an all-gather */
 #define LUTAMM_FLAG_OUTPUT_TILED  2u  /* write the output in the reference's DPU-tiled layout
                                          [dpu][f_mtile][n_in_stile][f_in_mtile] (pim_lut_kernel.c:183,
                                          test_amm.cpp:193-202) instead of row-major [M][N]          */
@@ -242,10 +244,23 @@ int lutamm_shard_finalize(lutamm_ctx* ctx);
 int lutamm_amm_column_sharded(lutamm_ctx* ctx, int layer_id, const float* input, float* gathered,
                               uint32_t n_tokens, uint32_t search_mode, uint32_t flags);
 
+/* The same with the exchange fused into the kernel (LUTAMM_FLAG_PEER_STORE): `gathered` must come from
+ * lutamm_shard_alloc_gathered, which allocates it on every rank (a collective call) and maps every rank's copy
+ * into every other rank through CUDA IPC.  The tcgen05 kernel's epilogue then stores each finished tile of this
+ * rank's slab into block `rank` of EVERY rank's buffer - plain stores over NVLink, no TMA, no multicast - so
+ * the transfer overlaps the contraction tile by tile; two small all-gathers order the ranks around it (nobody
+ * stores before everybody is done with the previous contents, nobody reads before everybody's kernel is done).
+ * Plans the fused kernel is not built for (CUDA-core gather, 64- or 256-wide tiles) fall back to the kernel
+ * plus all-gather.  The reference's counterpart is the per-DPU read-back of output slabs into one host
+ * tensor (src/host/pim_lut_host.cpp:173-203). */
+int lutamm_shard_alloc_gathered(lutamm_ctx* ctx, size_t bytes, void** device_ptr);
+int lutamm_shard_free_gathered(lutamm_ctx* ctx, void* device_ptr);
+
 /* Sharding by tokens (the reference's input_parallelism axis): weights replicated, rank r owns rows
  * [r*n/G, (r+1)*n/G) (n_tokens_total % G == 0), nothing is exchanged.  `input_rows` holds this rank's
  * rows.  gather == 0: `output` is this rank's [n/G][N] block.  gather != 0: `output` is the full
- * [n_tokens_total][N] on every rank, written in place by one all-gather.  Device buffers only. */
+ * [n_tokens_total][N] on every rank, written in place by one all-gather - or, with LUTAMM_FLAG_PEER_STORE and
+ * a buffer from lutamm_shard_alloc_gathered, by the kernel's own stores as above.  Device buffers only. */
 int lutamm_amm_token_sharded(lutamm_ctx* ctx, int layer_id, const float* input_rows, float* output,
                              uint32_t n_tokens_total, uint32_t gather, uint32_t flags);
 

@@ -18,7 +18,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libpimdl_b200.so")
 
 OK, EINVAL, ECUDA, ENOLAYER, EUNSUPPORTED, EDEVICE, ENOMEM = 0, -1, -2, -3, -4, -5, -6
-FLAG_ASYNC, FLAG_OUTPUT_TILED = 1, 2
+FLAG_ASYNC, FLAG_OUTPUT_TILED, FLAG_PEER_STORE = 1, 2, 4
 VARIANT_AUTO, VARIANT_GATHER, VARIANT_UMMA = 0, 1, 2
 INDEX_U8_ROWMAJOR, INDEX_U16_TILED = 0, 1
 LUT_CANONICAL, LUT_DPU_TILED = 0, 1
@@ -34,7 +34,7 @@ ABI_SYMBOLS = [
     "lutamm_load_weights_layout", "lutamm_measure_int8_peak",
     "lutamm_shard_unique_id", "lutamm_shard_init", "lutamm_shard_finalize", "lutamm_amm_column_sharded",
     "lutamm_amm_token_sharded", "lutamm_plan_cache_save", "lutamm_plan_cache_load",
-    "lutamm_selftest_bounded_wait",
+    "lutamm_selftest_bounded_wait", "lutamm_shard_alloc_gathered", "lutamm_shard_free_gathered",
 ]
 SHARD_SEARCH_REPLICATED, SHARD_SEARCH_SPLIT = 0, 1
 SHARD_ID_BYTES = 128
@@ -126,6 +126,8 @@ def load_library() -> ctypes.CDLL:
     L.lutamm_shard_finalize.argtypes = [vp]
     L.lutamm_amm_column_sharded.argtypes = [vp, i32, vp, vp, u32, u32, u32]
     L.lutamm_amm_token_sharded.argtypes = [vp, i32, vp, vp, u32, u32, u32]
+    L.lutamm_shard_alloc_gathered.argtypes = [vp, ctypes.c_size_t, ctypes.POINTER(vp)]
+    L.lutamm_shard_free_gathered.argtypes = [vp, vp]
     L.lutamm_selftest_bounded_wait.argtypes = [vp, u32]
     L.lutamm_plan_cache_save.argtypes = [vp, ctypes.c_char_p]
     L.lutamm_plan_cache_load.argtypes = [vp, ctypes.c_char_p]
@@ -329,6 +331,25 @@ class LutAmmContext:
         all-gather (the lut_parallelism axis of the reference, pim_lut_host.cpp:26-37)."""
         M = int(n_tokens if n_tokens is not None else input_tensor.shape[0])
         self._check(self._L.lutamm_amm_column_sharded(self._h, layer_id, _ptr(input_tensor), _ptr(gathered), M, search_mode, flags))
+
+    def shard_alloc_gathered(self, world: int, n_tokens: int, n_local: int):
+        """A gathered-output buffer [world][n_tokens][n_local] fp32 that every rank can store into (collective call;
+        CUDA IPC).  Returns a torch tensor view of it; release with shard_free_gathered(tensor)."""
+        import torch
+        nbytes = 4 * world * n_tokens * n_local
+        ptr = ctypes.c_void_p()
+        self._check(self._L.lutamm_shard_alloc_gathered(self._h, nbytes, ctypes.byref(ptr)))
+
+        class _Mem:   # the CUDA array interface lets torch wrap memory it did not allocate
+            __cuda_array_interface__ = {"shape": (world, n_tokens, n_local), "typestr": "<f4", "data": (ptr.value, False), "version": 3,
+                                        "strides": None}
+        holder = _Mem()
+        t = torch.as_tensor(holder, device=torch.device("cuda", self.device))
+        t._lutamm_base = ptr.value
+        return t
+
+    def shard_free_gathered(self, tensor):
+        self._check(self._L.lutamm_shard_free_gathered(self._h, ctypes.c_void_p(tensor._lutamm_base)))
 
     def amm_token_sharded(self, layer_id: int, input_rows, output, n_tokens_total: int, gather: bool = False, flags: int = 0):
         """This rank's tokens of the AMM (the input_parallelism axis, pim_lut_host.cpp:109-117); with gather=True

@@ -34,7 +34,14 @@ struct LutArgs {
     float scale, lut_bias;
     OutLayout layout;
     uint32_t act;         // LUTAMM_ACT_*: applied after the dequantisation
+    // Column sharding with the exchange fused into the kernel: the [M][N] block is also stored, by plain
+    // st.global over NVLink, at the same offsets of n_peers - 1 other GPUs' buffers (peer_out[g] points at
+    // this rank's block inside GPU g's gathered buffer; the entry for this GPU itself equals `out` and is
+    // skipped).  n_peers == 0: a purely local store.  tcgen05 variant, row-major output only.
+    uint32_t n_peers;
+    float* peer_out[8];
 };
+constexpr uint32_t kMaxPeers = 8;
 
 // Gather variant: LUT canonical [CB][CT][N] staged by 3-D TMA tiles.
 struct GatherPlan {

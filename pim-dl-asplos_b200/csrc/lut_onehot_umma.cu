@@ -114,7 +114,7 @@ __device__ __forceinline__ Item decode_item(const UmmaParams& p, uint32_t item, 
     return it;
 }
 
-template <uint32_t N_TILE, bool A_TMEM, uint32_t SPS>
+template <uint32_t N_TILE, bool A_TMEM, uint32_t SPS, bool PEER = false>
 __global__ void __launch_bounds__(kMaxThreads, 1)
 lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const UmmaParams p) {
     constexpr uint32_t kBBytes = N_TILE * kSlabK;
@@ -505,6 +505,15 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
 #pragma unroll
                                 for (uint32_t k = 0; k < 4; ++k)
                                     if (m_half + k * 4 < a.M) *reinterpret_cast<float4*>(orow + (size_t)k * 4 * a.N) = o[k];
+                                if constexpr (PEER) {  // the same rows into every other GPU's gathered buffer
+                                    for (uint32_t g = 0; g < a.n_peers; ++g) {
+                                        if (a.peer_out[g] == a.out) continue;
+                                        float* prow = a.peer_out[g] + (size_t)m_half * a.N + n;
+#pragma unroll
+                                        for (uint32_t k = 0; k < 4; ++k)
+                                            if (m_half + k * 4 < a.M) *reinterpret_cast<float4*>(prow + (size_t)k * 4 * a.N) = o[k];
+                                    }
+                                }
                             } else {
                                 for (uint32_t k = 0; k < 4; ++k) {
                                     const uint32_t mm = m_half + k * 4;
@@ -588,6 +597,11 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
                             }
                             if (!a.layout.tiled) {
                                 *reinterpret_cast<float4*>(a.out + (size_t)mm * a.N + n) = make_float4(o[0], o[1], o[2], o[3]);
+                                if constexpr (PEER) {
+                                    for (uint32_t g = 0; g < a.n_peers; ++g)
+                                        if (a.peer_out[g] != a.out)
+                                            *reinterpret_cast<float4*>(a.peer_out[g] + (size_t)mm * a.N + n) = make_float4(o[0], o[1], o[2], o[3]);
+                                }
                             } else {
 #pragma unroll
                                 for (uint32_t k = 0; k < 4; ++k) a.out[tiled_out_offset(mm, n + k, a.layout)] = o[k];
@@ -631,9 +645,9 @@ size_t umma_smem_bytes(uint32_t n_tile, uint32_t a_slots, uint32_t b_slots, bool
 constexpr size_t kSmemLimit = 227 * 1024;
 constexpr size_t kSmemOneCtaPerSm = 116 * 1024;  // of 228 KiB per SM
 
-template <uint32_t N_TILE, bool A_TMEM, uint32_t SPS>
+template <uint32_t N_TILE, bool A_TMEM, uint32_t SPS, bool PEER = false>
 cudaError_t run(const CUtensorMap& map, const UmmaParams& p, uint32_t grid, size_t smem, cudaStream_t s) {
-    auto k = lut_onehot_umma_kernel<N_TILE, A_TMEM, SPS>;
+    auto k = lut_onehot_umma_kernel<N_TILE, A_TMEM, SPS, PEER>;
     // Never two of these CTAs on one SM: the second would sit in tcgen05.alloc until the first has
     // freed its tensor memory, and with split tiles the first may be waiting for the second's slice.
     // The grid is at most one CTA per SM, but while the preceding kernel still holds some SMs
@@ -814,6 +828,14 @@ cudaError_t launch_umma(const LutArgs& a, const CUtensorMap& lut_t_map, const Um
     while (p.groups > 1 && p.a_slots % (p.groups * sps) != 0) --p.groups;
     if (split > 1 && (!acc_scratch || !tile_counters)) { *why = "tcgen05 variant: split > 1 needs scratch"; return cudaErrorInvalidValue; }
     const size_t smem = umma_smem_bytes(plan.n_tile, p.a_slots, p.b_slots, a_tmem);
+    if (a.n_peers) {
+        // the exchange fused into the epilogue: built for the tiles the default plans use
+        if (a.n_peers > kMaxPeers || a.layout.tiled) { *why = "tcgen05 variant: peer stores need row-major output and at most 8 GPUs"; return cudaErrorInvalidValue; }
+        if (plan.n_tile == 192 && a_tmem && sps == 1) return run<192, true, 1, true>(lut_t_map, p, grid, smem, s);
+        if (plan.n_tile == 128 && a_tmem && sps == 1) return run<128, true, 1, true>(lut_t_map, p, grid, smem, s);
+        *why = "tcgen05 variant: peer stores are built for 128- and 192-wide tiles with the one-hot operand in tensor memory";
+        return cudaErrorNotSupported;
+    }
 #define LUTAMM_UMMA_CASE(NT, TM, SP) \
     if (plan.n_tile == NT && a_tmem == TM && sps == SP) return run<NT, TM, SP>(lut_t_map, p, grid, smem, s);
     LUTAMM_UMMA_CASE(64, true, 1)

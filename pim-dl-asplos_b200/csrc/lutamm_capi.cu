@@ -87,6 +87,10 @@ struct lutamm_ctx {
     // sharding across the GPUs of a box (lutamm_shard_init)
     lutamm::NcclComm comm = nullptr;
     int rank = 0, world = 1;
+    // gathered-output buffers that every rank of the communicator can store into (lutamm_shard_alloc_gathered):
+    // local base -> this buffer as mapped here on each rank (entry [rank] is the local base itself)
+    std::map<void*, std::vector<void*>> peer_bufs;
+    Buf d_sync;  // a few words for the small all-gathers that order ranks around the peer stores
 };
 
 namespace {
@@ -191,8 +195,12 @@ int check_tiled(lutamm_ctx* c, const Layer& L, uint32_t M) {
 
 // step 2+3 on device buffers
 int run_lut(lutamm_ctx* c, Layer& L, const uint8_t* d_idx, float* d_out, int32_t* d_acc_out, uint32_t M,
-            uint32_t flags, const lutamm_plan& plan) {
+            uint32_t flags, const lutamm_plan& plan, float* const* peer_out = nullptr, uint32_t n_peers = 0) {
     LutArgs a{};
+    if (peer_out && n_peers && n_peers <= kMaxPeers) {
+        a.n_peers = n_peers;
+        for (uint32_t g = 0; g < n_peers; ++g) a.peer_out[g] = peer_out[g];
+    }
     a.idx = d_idx;
     a.bias = L.d_bias;
     a.out = d_out;
@@ -248,10 +256,12 @@ int run_lut(lutamm_ctx* c, Layer& L, const uint8_t* d_idx, float* d_out, int32_t
         }
         cudaError_t e = launch_umma(a, L.umma_maps[slot], up, static_cast<int32_t*>(c->d_acc_scratch.p),
                                     static_cast<uint32_t*>(c->d_counters.p), c->d_err, c->stream, &why);
+        if (e == cudaErrorNotSupported && a.n_peers) return fail(c, LUTAMM_EUNSUPPORTED, why ? why : "peer stores not built for this plan");
         if (e != cudaSuccess) return fail(c, LUTAMM_ECUDA, why ? why : (std::string("tcgen05 launch: ") + cudaGetErrorString(e)));
         ++c->launches;
         return LUTAMM_OK;
     }
+    if (a.n_peers) return fail(c, LUTAMM_EUNSUPPORTED, "peer stores exist in the tcgen05 kernel only");
     if (variant != LUTAMM_VARIANT_GATHER) return fail(c, LUTAMM_EINVAL, "unknown kernel variant");
     uint32_t cfg = plan.gather_cfg;
     if (cfg >= gather_num_cfgs()) return fail(c, LUTAMM_EINVAL, "unknown gather tile configuration");
@@ -463,6 +473,13 @@ int lutamm_destroy(lutamm_ctx* c) {
     if (c->s_in) cudaStreamSynchronize(c->s_in);
     cudaStreamSynchronize(c->stream);
     if (c->s_out) cudaStreamSynchronize(c->s_out);
+    for (auto& kv : c->peer_bufs) {
+        for (size_t g = 0; g < kv.second.size(); ++g)
+            if ((int)g != c->rank && kv.second[g]) cudaIpcCloseMemHandle(kv.second[g]);
+        cudaFree(kv.first);
+    }
+    c->peer_bufs.clear();
+    cudaFree(c->d_sync.p);
     if (c->comm && nccl_api().ok) nccl_api().comm_destroy(c->comm);
     c->comm = nullptr;
     for (auto& kv : c->layers) free_layer(kv.second);
@@ -938,6 +955,85 @@ int lutamm_shard_finalize(lutamm_ctx* c) {
     return LUTAMM_OK;
 }
 
+// A small all-gather on the context's stream: a rank passes it only after every rank has reached it in its own
+// stream order.  Orders the ranks' kernels around stores into one another's memory.
+static int rank_barrier(lutamm_ctx* c) {
+    if (c->world <= 1) return LUTAMM_OK;
+    const NcclApi& n = nccl_api();
+    int rc;
+    if ((rc = ensure(c, c->d_sync, 4 * (size_t)c->world, true))) return rc;
+    uint32_t* w = static_cast<uint32_t*>(c->d_sync.p);
+    const int e = n.all_gather(w + c->rank, w, 4, kNcclUint8, c->comm, c->stream);
+    if (e != kNcclSuccess) return fail(c, LUTAMM_ECUDA, std::string("ncclAllGather(barrier): ") + n.get_error_string(e));
+    return LUTAMM_OK;
+}
+
+int lutamm_shard_alloc_gathered(lutamm_ctx* c, size_t bytes, void** out) {
+    if (!c) return fail(nullptr, LUTAMM_EINVAL, "null context");
+    if (!out || !bytes) return fail(c, LUTAMM_EINVAL, "null out pointer or zero size");
+    *out = nullptr;
+    DeviceGuard g(c->device);
+    const int G = c->world, r = c->rank;
+    if (G > (int)kMaxPeers) return fail(c, LUTAMM_EUNSUPPORTED, "at most 8 ranks");
+    if (G > 1 && !c->comm) return fail(c, LUTAMM_EINVAL, "lutamm_shard_init has not been called on this context");
+    void* p = nullptr;
+    cudaError_t ce = cudaMalloc(&p, bytes);
+    if (ce != cudaSuccess) return fail(c, LUTAMM_ENOMEM, std::string("cudaMalloc(gathered): ") + cudaGetErrorString(ce));
+    std::vector<void*> peers((size_t)G, nullptr);
+    peers[(size_t)r] = p;
+    if (G > 1) {
+        // every rank's CUDA IPC handle to every rank: 64 bytes each through one all-gather
+        const NcclApi& n = nccl_api();
+        constexpr size_t H = sizeof(cudaIpcMemHandle_t);
+        cudaIpcMemHandle_t mine;
+        std::vector<cudaIpcMemHandle_t> all((size_t)G);
+        int rc = ensure(c, c->d_build, H * (size_t)G + 256);
+        bool ok = rc == LUTAMM_OK;
+        unsigned char* st = static_cast<unsigned char*>(c->d_build.p);
+        if (ok && (ce = cudaIpcGetMemHandle(&mine, p)) != cudaSuccess) { ok = false; rc = fail(c, LUTAMM_ECUDA, std::string("cudaIpcGetMemHandle: ") + cudaGetErrorString(ce)); }
+        if (ok && (ce = cudaMemcpyAsync(st + H * r, &mine, H, cudaMemcpyHostToDevice, c->stream)) != cudaSuccess) { ok = false; rc = fail(c, LUTAMM_ECUDA, cudaGetErrorString(ce)); }
+        if (ok) {
+            const int e = n.all_gather(st + H * r, st, H, kNcclUint8, c->comm, c->stream);
+            if (e != kNcclSuccess) { ok = false; rc = fail(c, LUTAMM_ECUDA, std::string("ncclAllGather(handles): ") + n.get_error_string(e)); }
+        }
+        if (ok && ((ce = cudaMemcpyAsync(all.data(), st, H * G, cudaMemcpyDeviceToHost, c->stream)) != cudaSuccess ||
+                   (ce = cudaStreamSynchronize(c->stream)) != cudaSuccess)) { ok = false; rc = fail(c, LUTAMM_ECUDA, cudaGetErrorString(ce)); }
+        for (int q = 0; ok && q < G; ++q) {
+            if (q == r) continue;
+            if ((ce = cudaIpcOpenMemHandle(&peers[(size_t)q], all[(size_t)q], cudaIpcMemLazyEnablePeerAccess)) != cudaSuccess) {
+                ok = false;
+                rc = fail(c, LUTAMM_ECUDA, std::string("cudaIpcOpenMemHandle (is peer access between the GPUs available?): ") + cudaGetErrorString(ce));
+            }
+        }
+        if (!ok) {
+            for (int q = 0; q < G; ++q)
+                if (q != r && peers[(size_t)q]) cudaIpcCloseMemHandle(peers[(size_t)q]);
+            cudaFree(p);
+            return rc;
+        }
+    }
+    c->peer_bufs[p] = peers;
+    *out = p;
+    return LUTAMM_OK;
+}
+
+int lutamm_shard_free_gathered(lutamm_ctx* c, void* ptr) {
+    if (!c) return fail(nullptr, LUTAMM_EINVAL, "null context");
+    DeviceGuard g(c->device);
+    auto it = c->peer_bufs.find(ptr);
+    if (it == c->peer_bufs.end()) return fail(c, LUTAMM_EINVAL, "not a buffer from lutamm_shard_alloc_gathered");
+    int rc = rank_barrier(c);  // nobody stores into anybody's buffer any more
+    if (rc) return rc;
+    CU_TRY(c, cudaStreamSynchronize(c->stream));
+    for (size_t q = 0; q < it->second.size(); ++q)
+        if ((int)q != c->rank && it->second[q]) cudaIpcCloseMemHandle(it->second[q]);
+    if ((rc = rank_barrier(c))) return rc;   // every rank has unmapped before anybody frees
+    CU_TRY(c, cudaStreamSynchronize(c->stream));
+    cudaFree(ptr);
+    c->peer_bufs.erase(it);
+    return LUTAMM_OK;
+}
+
 int lutamm_amm_column_sharded(lutamm_ctx* c, int layer_id, const float* input, float* gathered, uint32_t M,
                               uint32_t search_mode, uint32_t flags) {
     if (!c) return fail(nullptr, LUTAMM_EINVAL, "null context");
@@ -967,8 +1063,28 @@ int lutamm_amm_column_sharded(lutamm_ctx* c, int layer_id, const float* input, f
     } else {
         if ((rc = run_ccs(c, *L, input, d_idx, M, LUTAMM_INDEX_U8_ROWMAJOR))) return rc;
     }
-    // this rank's [M][N_loc] slab straight into block r of the gathered buffer, then the blocks in place
     const size_t slab = (size_t)M * L->N;
+    if ((flags & LUTAMM_FLAG_PEER_STORE) && G > 1) {
+        // The exchange fused into the kernel: the epilogue stores every finished tile of this rank's slab into
+        // block r of EVERY rank's gathered buffer (plain stores over NVLink to memory mapped by CUDA IPC), so the
+        // transfer overlaps the contraction tile by tile and no all-gather follows.  A rank may only start storing
+        // once every rank is done with the buffer's previous contents, and may only read once every rank's kernel
+        // has finished: one small all-gather before and one after.
+        auto pb = c->peer_bufs.find(gathered);
+        if (pb == c->peer_bufs.end()) return fail(c, LUTAMM_EINVAL, "LUTAMM_FLAG_PEER_STORE needs a buffer from lutamm_shard_alloc_gathered");
+        float* peer_out[kMaxPeers] = {};
+        for (uint32_t q = 0; q < G; ++q) peer_out[q] = static_cast<float*>(pb->second[q]) + (size_t)r * slab;
+        if ((rc = rank_barrier(c))) return rc;
+        rc = run_lut(c, *L, d_idx, gathered + (size_t)r * slab, nullptr, M, 0, L->plan, peer_out, G);
+        if (rc == LUTAMM_OK) {
+            if ((rc = rank_barrier(c))) return rc;
+            if (flags & LUTAMM_FLAG_ASYNC) return LUTAMM_OK;
+            return check_dev_err(c);
+        }
+        if (rc != LUTAMM_EUNSUPPORTED) return rc;
+        // this plan has no fused form: the plain kernel and an all-gather, below
+    }
+    // this rank's [M][N_loc] slab straight into block r of the gathered buffer, then the blocks in place
     if ((rc = run_lut(c, *L, d_idx, gathered + (size_t)r * slab, nullptr, M, 0, L->plan))) return rc;
     if (G > 1) {
         const int e = n.all_gather(gathered + (size_t)r * slab, gathered, slab, kNcclFloat32, c->comm, c->stream);
@@ -997,6 +1113,21 @@ int lutamm_amm_token_sharded(lutamm_ctx* c, int layer_id, const float* input_row
     float* mine = gather ? output + (size_t)r * m_loc * L->N : output;
     if (reinterpret_cast<uintptr_t>(mine) & 15u) return fail(c, LUTAMM_EINVAL, "device output must be 16-byte aligned");
     if ((rc = run_ccs(c, *L, input_rows, c->d_idx.p, m_loc, LUTAMM_INDEX_U8_ROWMAJOR))) return rc;
+    if (gather && G > 1 && (flags & LUTAMM_FLAG_PEER_STORE)) {
+        // the row blocks exchanged by the kernel's own stores (see lutamm_amm_column_sharded)
+        auto pb = c->peer_bufs.find(output);
+        if (pb == c->peer_bufs.end()) return fail(c, LUTAMM_EINVAL, "LUTAMM_FLAG_PEER_STORE needs a buffer from lutamm_shard_alloc_gathered");
+        float* peer_out[kMaxPeers] = {};
+        for (uint32_t q = 0; q < G; ++q) peer_out[q] = static_cast<float*>(pb->second[q]) + (size_t)r * m_loc * L->N;
+        if ((rc = rank_barrier(c))) return rc;
+        rc = run_lut(c, *L, static_cast<const uint8_t*>(c->d_idx.p), mine, nullptr, m_loc, 0, L->plan, peer_out, G);
+        if (rc == LUTAMM_OK) {
+            if ((rc = rank_barrier(c))) return rc;
+            if (flags & LUTAMM_FLAG_ASYNC) return LUTAMM_OK;
+            return check_dev_err(c);
+        }
+        if (rc != LUTAMM_EUNSUPPORTED) return rc;
+    }
     if ((rc = run_lut(c, *L, static_cast<const uint8_t*>(c->d_idx.p), mine, nullptr, m_loc, 0, L->plan))) return rc;
     if (gather && G > 1) {
         const NcclApi& n = nccl_api();

@@ -47,7 +47,37 @@ def main():
             flat = gathered.reshape(-1).cpu().numpy()
             ref = np.array([want[i, j] for i in (0, M - 1) for j in (0, n_loc, N - 1)])
             assert np.array_equal(flat[offs].view(np.uint32), ref.view(np.uint32)), "not the reference's tiled layout"
+    # ---- columns, the exchange fused into the kernel: every rank stores its slab into every rank's buffer
+    ctx.set_plan(0, variant=P.VARIANT_AUTO)
+    gbuf = ctx.shard_alloc_gathered(world, M, n_loc)
+    for it in range(3):
+        gbuf.fill_(float("nan"))
+        torch.cuda.synchronize()
+        ctx.amm_column_sharded(0, x, gbuf, n_tokens=M, search_mode=P.SHARD_SEARCH_SPLIT, flags=P.FLAG_PEER_STORE)
+        got = gbuf.permute(1, 0, 2).reshape(M, N).cpu().numpy()
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), (rank, it, "column-sharded, peer stores")
+        dist.barrier()   # nobody refills its buffer while a peer may still be checking... its own copy only, but keep the ranks in step
+    ctx.set_plan(0, variant=P.VARIANT_GATHER)   # no fused form: falls back to kernel + all-gather
+    gbuf.fill_(float("nan"))
+    torch.cuda.synchronize()
+    ctx.amm_column_sharded(0, x, gbuf, n_tokens=M, flags=P.FLAG_PEER_STORE)
+    assert np.array_equal(gbuf.permute(1, 0, 2).reshape(M, N).cpu().numpy().view(np.uint32), want.view(np.uint32)), "fallback"
+    ctx.shard_free_gathered(gbuf)
     ctx.unload_weights(0)
+    # a long codebook axis, so that tiles are split across CTAs and the summing pass does the peer stores
+    c2 = synth.make_case(M=256 * world, K=2048, N=256 * world, v=2, CT=16, seed=4)
+    want2 = oracle.amm(c2.x, c2.centroid, c2.lut, c2.bias, c2.scale, 0.0)[0]
+    lo2, hi2 = shard.column_range(c2.N, rank, world)
+    ctx.load_weights(2, c2.centroid, np.ascontiguousarray(c2.lut[:, :, lo2:hi2]), np.ascontiguousarray(c2.bias[lo2:hi2]), c2.scale)
+    ctx.set_plan(2, variant=P.VARIANT_UMMA, umma_n_tile=128, umma_split=4)
+    g2 = ctx.shard_alloc_gathered(world, c2.M, hi2 - lo2)
+    g2.fill_(float("nan"))
+    torch.cuda.synchronize()
+    ctx.amm_column_sharded(2, torch.from_numpy(c2.x).cuda(), g2, n_tokens=c2.M, flags=P.FLAG_PEER_STORE)
+    got2 = g2.permute(1, 0, 2).reshape(c2.M, c2.N).cpu().numpy()
+    assert np.array_equal(got2.view(np.uint32), want2.view(np.uint32)), (rank, "peer stores, split tiles")
+    ctx.shard_free_gathered(g2)
+    ctx.unload_weights(2)
     # ---- tokens: weights replicated
     ctx.load_weights(1, c.centroid, c.lut, c.bias, c.scale)
     m_lo, m_hi = shard.token_range(M, rank, world)
@@ -57,6 +87,12 @@ def main():
     full = torch.full((M, N), float("nan"), device="cuda")
     ctx.amm_token_sharded(1, x[m_lo:m_hi].contiguous(), full, M, gather=True)
     assert np.array_equal(full.cpu().numpy().view(np.uint32), want.view(np.uint32)), (rank, "token-sharded + gather")
+    gfull = ctx.shard_alloc_gathered(1, M, N)          # [1][M][N]: the full output, storable by every rank
+    gfull.fill_(float("nan"))
+    torch.cuda.synchronize()
+    ctx.amm_token_sharded(1, x[m_lo:m_hi].contiguous(), gfull, M, gather=True, flags=P.FLAG_PEER_STORE)
+    assert np.array_equal(gfull[0].cpu().numpy().view(np.uint32), want.view(np.uint32)), (rank, "token-sharded, peer stores")
+    ctx.shard_free_gathered(gfull)
     ctx.shard_finalize()
     ctx.close()
     dist.barrier()
