@@ -114,3 +114,36 @@ def test_gpu_build_lut_rejects_bad_shapes(ctx):
     assert e.value.code == P.EINVAL
     with pytest.raises(P.LutAmmError):   # one codebook's centroids must fit 48 KB of shared memory
         ctx.build_lut(np.zeros((1, 256, 64), np.float32), np.zeros((64, 16), np.float32))
+
+
+def test_layer_loader_reads_what_the_converters_write():
+    """The layer loader against the reference converter's own output file (no GPU needed): a converted
+    checkpoint holds the three projections query / key / value - there is no fused qkv operator in it - so the
+    layer is loaded with separate Q / K / V operators (the reference's SEPARATE build reads the same keys,
+    test/test_transformer.cpp:295-368), with the attention-output operator's codebook settings
+    (src/host/parser.cpp:235-322)."""
+    from pim_dl_asplos_b200 import layer as L
+    _, ref = fixtures()
+    D, F = FEATURES, 4 * FEATURES
+    cb = {"qkv": 16, "o": 16, "ffn1": 16, "ffn2": 64}
+    ct = {k: NCENT for k in cb}
+    w = L.load_layer_weights_npz(ref, 0, D, F, cb, ct)
+    assert set(w) == {"q", "k", "v", "o", "ffn1", "ffn2", "ln1", "ln2"}
+    for name, (K, N, CB) in {"q": (D, D, 16), "k": (D, D, 16), "v": (D, D, 16), "o": (D, D, 16), "ffn1": (D, F, 16), "ffn2": (F, D, 64)}.items():
+        cen, lut, bias, scale, lut_bias = w[name]
+        assert cen.shape == (CB, NCENT, K // CB) and lut.shape == (CB, NCENT, N) and lut.dtype == np.int8 and bias.shape == (N,)
+        assert scale > 0 and lut_bias == 0.0
+    assert np.array_equal(w["q"][1].reshape(-1, D), ref["0.attention.self.query.lut.tensor"])
+    assert L.checkpoint_layer_count(ref) == 1
+    with pytest.raises(KeyError):
+        L.load_layer_weights_npz(ref, 0, D, F, cb, ct, separate_qkv=False)      # no fused operator in this file
+    with pytest.raises(ValueError):
+        L.load_layer_weights_npz(ref, 0, D, F, dict(cb, o=8), ct)               # wrong codebook count
+    # a file with a fused operator loads as one
+    fused = dict(ref)
+    for suffix in ("centroids.weight", "lut.scale", "lut.bias"):
+        fused["0.attention.self.qkv." + suffix] = ref["0.attention.self.query." + suffix]
+    fused["0.attention.self.qkv.lut.tensor"] = np.concatenate([ref[f"0.attention.self.{n}.lut.tensor"] for n in ("query", "key", "value")], axis=1)
+    fused["0.attention.self.qkv.bias"] = np.concatenate([ref[f"0.attention.self.{n}.bias"] for n in ("query", "key", "value")])
+    w2 = L.load_layer_weights_npz(fused, 0, D, F, cb, ct)
+    assert "qkv" in w2 and w2["qkv"][1].shape == (16, NCENT, 3 * D)
