@@ -732,10 +732,15 @@ def leg_c5_sharded(ctx, stream, m_total, rank, world, P, synth, torch, dist, ora
     out["m"] = {"ms": ms, "tokens_per_s": m_total / (ms * 1e-3), "collective_ms": 0.0, "relayout_ms": 0.0, "parity_ok": all_ok(ok),
                 "what": "tokens split, weights replicated, output stays sharded"}
     del y_m
-    ctx.unload_weights(910)
     # ---- (n) output columns
     ctx.load_weights(911, cen, lut[:, :, rank * n_loc:(rank + 1) * n_loc].contiguous(), bias[rank * n_loc:(rank + 1) * n_loc].contiguous(), 0.01, 0.0)
     del lut
+    # the library's own pick among the shardings that leave the whole output on every rank (lutamm_tune_sharding)
+    try:
+        out["tuner"] = ctx.tune_sharding(910, 911, m_total, reps=2)
+    except P.LutAmmError as ex:
+        out["tuner"] = {"error": str(ex)[:200]}
+    ctx.unload_weights(910)
     y_all = torch.empty(world, m_total, n_loc, device="cuda", dtype=torch.float32)
     res = {}
     for name, mode in (("search_replicated", P.SHARD_SEARCH_REPLICATED), ("search_split", P.SHARD_SEARCH_SPLIT)):

@@ -251,7 +251,8 @@ int lutamm_amm_column_sharded(lutamm_ctx* ctx, int layer_id, const float* input,
  * the transfer overlaps the contraction tile by tile; two small all-gathers order the ranks around it (nobody
  * stores before everybody is done with the previous contents, nobody reads before everybody's kernel is done).
  * Plans the fused kernel is not built for (CUDA-core gather, 64- or 256-wide tiles) fall back to the kernel
- * plus all-gather.  The reference's counterpart is the per-DPU read-back of output slabs into one host
+ * plus all-gather.  A rank whose allocation fails still takes part in the handle exchange, so every rank
+ * returns LUTAMM_ENOMEM together instead of some waiting for it.  The reference's counterpart is the per-DPU read-back of output slabs into one host
  * tensor (src/host/pim_lut_host.cpp:173-203). */
 int lutamm_shard_alloc_gathered(lutamm_ctx* ctx, size_t bytes, void** device_ptr);
 int lutamm_shard_free_gathered(lutamm_ctx* ctx, void* device_ptr);
@@ -263,6 +264,31 @@ int lutamm_shard_free_gathered(lutamm_ctx* ctx, void* device_ptr);
  * a buffer from lutamm_shard_alloc_gathered, by the kernel's own stores as above.  Device buffers only. */
 int lutamm_amm_token_sharded(lutamm_ctx* ctx, int layer_id, const float* input_rows, float* output,
                              uint32_t n_tokens_total, uint32_t gather, uint32_t flags);
+
+/* Which sharding of ONE operator is fastest on this group of GPUs (the reference's auto-tuner ranks
+ * input_parallelism x lut_parallelism splits of an AMM by a latency model, src/tuner/auto_tuner.cpp:368-549; here
+ * the candidates are timed).  A collective call: every rank passes the same n_tokens_total (a multiple of the
+ * world size) and the same reps.  `layer_all_columns` holds the operator with all N output columns (token
+ * sharding), `layer_my_columns` this rank's N/G columns of it (column sharding); either may be negative to
+ * leave its candidates out.  The call allocates its own operands (input n_tokens_total x K, one gathered buffer of
+ * n_tokens_total x N floats through lutamm_shard_alloc_gathered), times `reps` calls of each candidate with CUDA events
+ * after two warm-up calls, and reports the slowest rank's time per call in ms[], -1 for a candidate that was
+ * left out or that this build has no kernel for.  `best` is the fastest candidate that leaves the whole output on
+ * every rank (LUTAMM_SHARDING_TOKENS_LOCAL, which gathers nothing, is reported for comparison only). */
+#define LUTAMM_SHARDING_TOKENS_LOCAL     0u  /* lutamm_amm_token_sharded, gather = 0                     */
+#define LUTAMM_SHARDING_TOKENS_GATHERED  1u  /* ... gather = 1: rows all-gathered                         */
+#define LUTAMM_SHARDING_TOKENS_FUSED     2u  /* ... gather = 1 with LUTAMM_FLAG_PEER_STORE                 */
+#define LUTAMM_SHARDING_COLUMNS          3u  /* lutamm_amm_column_sharded, LUTAMM_SHARD_SEARCH_REPLICATED  */
+#define LUTAMM_SHARDING_COLUMNS_SPLIT    4u  /* ... LUTAMM_SHARD_SEARCH_SPLIT                             */
+#define LUTAMM_SHARDING_COLUMNS_FUSED    5u  /* ... LUTAMM_SHARD_SEARCH_SPLIT with LUTAMM_FLAG_PEER_STORE  */
+#define LUTAMM_SHARDING_MODES            6
+typedef struct {
+    uint32_t best;
+    uint32_t world;
+    float ms[LUTAMM_SHARDING_MODES];
+} lutamm_sharding_report;
+int lutamm_tune_sharding(lutamm_ctx* ctx, int layer_all_columns, int layer_my_columns, uint32_t n_tokens_total,
+                         uint32_t reps, lutamm_sharding_report* report);
 
 /* ---- plans, tuning, timing ------------------------------------------------------- */
 

@@ -33,7 +33,7 @@ ABI_SYMBOLS = [
     "lutamm_amm_static_scratch", "lutamm_static_scratch_last_error", "lutamm_build_lut",
     "lutamm_load_weights_layout", "lutamm_measure_int8_peak",
     "lutamm_shard_unique_id", "lutamm_shard_init", "lutamm_shard_finalize", "lutamm_amm_column_sharded",
-    "lutamm_amm_token_sharded", "lutamm_plan_cache_save", "lutamm_plan_cache_load",
+    "lutamm_amm_token_sharded", "lutamm_tune_sharding", "lutamm_plan_cache_save", "lutamm_plan_cache_load",
     "lutamm_selftest_bounded_wait", "lutamm_shard_alloc_gathered", "lutamm_shard_free_gathered",
 ]
 SHARD_SEARCH_REPLICATED, SHARD_SEARCH_SPLIT = 0, 1
@@ -75,6 +75,13 @@ class Plan(ctypes.Structure):
     def as_dict(self):
         return {k: getattr(self, k) for k in ("variant", "ccs_tokens", "gather_cfg", "umma_n_tile", "umma_split",
                                               "umma_stages", "umma_groups", "umma_operand", "umma_sps")}
+
+
+SHARDING_MODES = ("tokens_local", "tokens_gathered", "tokens_fused", "columns", "columns_split", "columns_fused")
+
+
+class ShardingReport(ctypes.Structure):
+    _fields_ = [("best", ctypes.c_uint32), ("world", ctypes.c_uint32), ("ms", ctypes.c_float * len(SHARDING_MODES))]
 
 
 class Timings(ctypes.Structure):
@@ -126,6 +133,7 @@ def load_library() -> ctypes.CDLL:
     L.lutamm_shard_finalize.argtypes = [vp]
     L.lutamm_amm_column_sharded.argtypes = [vp, i32, vp, vp, u32, u32, u32]
     L.lutamm_amm_token_sharded.argtypes = [vp, i32, vp, vp, u32, u32, u32]
+    L.lutamm_tune_sharding.argtypes = [vp, i32, i32, u32, u32, ctypes.POINTER(ShardingReport)]
     L.lutamm_shard_alloc_gathered.argtypes = [vp, ctypes.c_size_t, ctypes.POINTER(vp)]
     L.lutamm_shard_free_gathered.argtypes = [vp, vp]
     L.lutamm_selftest_bounded_wait.argtypes = [vp, u32]
@@ -356,6 +364,15 @@ class LutAmmContext:
         `output` is the full [n_tokens_total][N] on every rank."""
         self._check(self._L.lutamm_amm_token_sharded(self._h, layer_id, _ptr(input_rows), _ptr(output), n_tokens_total,
                                                      1 if gather else 0, flags))
+
+    def tune_sharding(self, layer_all_columns: int, layer_my_columns: int, n_tokens_total: int, reps: int = 3) -> dict:
+        """Times the shardings of one operator on this group of GPUs (a collective call; the auto-tuner's choice of
+        input_parallelism x lut_parallelism, auto_tuner.cpp:368-549, by measurement).  Pass -1 for a layer that is not
+        loaded.  Returns {"best": name, "world": G, "ms": {name: ms per call of the slowest rank, or None}}."""
+        r = ShardingReport()
+        self._check(self._L.lutamm_tune_sharding(self._h, layer_all_columns, layer_my_columns, n_tokens_total, reps, ctypes.byref(r)))
+        return {"best": SHARDING_MODES[r.best], "world": int(r.world),
+                "ms": {n: (float(r.ms[i]) if r.ms[i] >= 0 else None) for i, n in enumerate(SHARDING_MODES)}}
 
     # -- plans / tuning / timing
     def set_plan(self, layer_id: int, **kw):

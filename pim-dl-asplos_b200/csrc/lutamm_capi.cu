@@ -65,6 +65,7 @@ struct Buf {
 struct lutamm_ctx {
     int device = 0;
     int sm_count = 148;
+    uint64_t unfused_exchanges = 0;  // sharded calls that asked for peer stores and got the kernel + all-gather
     cudaStream_t own_stream = nullptr;
     cudaStream_t stream = nullptr;
     std::map<int, Layer> layers;
@@ -978,19 +979,27 @@ int lutamm_shard_alloc_gathered(lutamm_ctx* c, size_t bytes, void** out) {
     if (G > 1 && !c->comm) return fail(c, LUTAMM_EINVAL, "lutamm_shard_init has not been called on this context");
     void* p = nullptr;
     cudaError_t ce = cudaMalloc(&p, bytes);
-    if (ce != cudaSuccess) return fail(c, LUTAMM_ENOMEM, std::string("cudaMalloc(gathered): ") + cudaGetErrorString(ce));
+    if (ce != cudaSuccess) {
+        p = nullptr;
+        cudaGetLastError();
+        if (G == 1) return fail(c, LUTAMM_ENOMEM, std::string("cudaMalloc(gathered): ") + cudaGetErrorString(ce));
+    }
     std::vector<void*> peers((size_t)G, nullptr);
     peers[(size_t)r] = p;
     if (G > 1) {
-        // every rank's CUDA IPC handle to every rank: 64 bytes each through one all-gather
+        // every rank's CUDA IPC handle to every rank, with a word that says whether the rank has a buffer at all
+        // (a rank whose allocation failed still takes part, so that all ranks leave together): one all-gather
         const NcclApi& n = nccl_api();
-        constexpr size_t H = sizeof(cudaIpcMemHandle_t);
-        cudaIpcMemHandle_t mine;
-        std::vector<cudaIpcMemHandle_t> all((size_t)G);
+        struct Slot { cudaIpcMemHandle_t handle; uint32_t valid; uint32_t pad[3]; };
+        static_assert(sizeof(Slot) % 16 == 0, "slot size");
+        constexpr size_t H = sizeof(Slot);
+        Slot mine{};
+        std::vector<Slot> all((size_t)G);
         int rc = ensure(c, c->d_build, H * (size_t)G + 256);
-        bool ok = rc == LUTAMM_OK;
+        bool ok = rc == LUTAMM_OK;   // (a failure here or in the exchange itself is not agreed on: the group is unusable)
         unsigned char* st = static_cast<unsigned char*>(c->d_build.p);
-        if (ok && (ce = cudaIpcGetMemHandle(&mine, p)) != cudaSuccess) { ok = false; rc = fail(c, LUTAMM_ECUDA, std::string("cudaIpcGetMemHandle: ") + cudaGetErrorString(ce)); }
+        cudaError_t he = cudaSuccess;
+        if (p && (he = cudaIpcGetMemHandle(&mine.handle, p)) == cudaSuccess) mine.valid = 1;
         if (ok && (ce = cudaMemcpyAsync(st + H * r, &mine, H, cudaMemcpyHostToDevice, c->stream)) != cudaSuccess) { ok = false; rc = fail(c, LUTAMM_ECUDA, cudaGetErrorString(ce)); }
         if (ok) {
             const int e = n.all_gather(st + H * r, st, H, kNcclUint8, c->comm, c->stream);
@@ -998,9 +1007,16 @@ int lutamm_shard_alloc_gathered(lutamm_ctx* c, size_t bytes, void** out) {
         }
         if (ok && ((ce = cudaMemcpyAsync(all.data(), st, H * G, cudaMemcpyDeviceToHost, c->stream)) != cudaSuccess ||
                    (ce = cudaStreamSynchronize(c->stream)) != cudaSuccess)) { ok = false; rc = fail(c, LUTAMM_ECUDA, cudaGetErrorString(ce)); }
+        for (int q = 0; ok && q < G; ++q)
+            if (!all[(size_t)q].valid) {
+                ok = false;
+                rc = q == r ? fail(c, p ? LUTAMM_ECUDA : LUTAMM_ENOMEM, p ? std::string("cudaIpcGetMemHandle: ") + cudaGetErrorString(he)
+                                                                          : std::string("cudaMalloc(gathered) failed on this rank"))
+                            : fail(c, LUTAMM_ENOMEM, "rank " + std::to_string(q) + " could not allocate its gathered buffer");
+            }
         for (int q = 0; ok && q < G; ++q) {
             if (q == r) continue;
-            if ((ce = cudaIpcOpenMemHandle(&peers[(size_t)q], all[(size_t)q], cudaIpcMemLazyEnablePeerAccess)) != cudaSuccess) {
+            if ((ce = cudaIpcOpenMemHandle(&peers[(size_t)q], all[(size_t)q].handle, cudaIpcMemLazyEnablePeerAccess)) != cudaSuccess) {
                 ok = false;
                 rc = fail(c, LUTAMM_ECUDA, std::string("cudaIpcOpenMemHandle (is peer access between the GPUs available?): ") + cudaGetErrorString(ce));
             }
@@ -1008,7 +1024,7 @@ int lutamm_shard_alloc_gathered(lutamm_ctx* c, size_t bytes, void** out) {
         if (!ok) {
             for (int q = 0; q < G; ++q)
                 if (q != r && peers[(size_t)q]) cudaIpcCloseMemHandle(peers[(size_t)q]);
-            cudaFree(p);
+            if (p) cudaFree(p);
             return rc;
         }
     }
@@ -1082,7 +1098,7 @@ int lutamm_amm_column_sharded(lutamm_ctx* c, int layer_id, const float* input, f
             return check_dev_err(c);
         }
         if (rc != LUTAMM_EUNSUPPORTED) return rc;
-        // this plan has no fused form: the plain kernel and an all-gather, below
+        ++c->unfused_exchanges;  // this plan has no fused form: the plain kernel and an all-gather, below
     }
     // this rank's [M][N_loc] slab straight into block r of the gathered buffer, then the blocks in place
     if ((rc = run_lut(c, *L, d_idx, gathered + (size_t)r * slab, nullptr, M, 0, L->plan))) return rc;
@@ -1127,6 +1143,7 @@ int lutamm_amm_token_sharded(lutamm_ctx* c, int layer_id, const float* input_row
             return check_dev_err(c);
         }
         if (rc != LUTAMM_EUNSUPPORTED) return rc;
+        ++c->unfused_exchanges;
     }
     if ((rc = run_lut(c, *L, static_cast<const uint8_t*>(c->d_idx.p), mine, nullptr, m_loc, 0, L->plan))) return rc;
     if (gather && G > 1) {
@@ -1136,6 +1153,113 @@ int lutamm_amm_token_sharded(lutamm_ctx* c, int layer_id, const float* input_row
     }
     if (flags & LUTAMM_FLAG_ASYNC) return LUTAMM_OK;
     return check_dev_err(c);
+}
+
+int lutamm_tune_sharding(lutamm_ctx* c, int layer_all, int layer_cols, uint32_t M, uint32_t reps, lutamm_sharding_report* rep) {
+    if (!c) return fail(nullptr, LUTAMM_EINVAL, "null context");
+    if (!rep) return fail(c, LUTAMM_EINVAL, "null report");
+    DeviceGuard g(c->device);
+    const uint32_t G = (uint32_t)c->world;
+    if (G > 1 && !c->comm) return fail(c, LUTAMM_EINVAL, "lutamm_shard_init has not been called on this context");
+    if (M == 0 || M % G) return fail(c, LUTAMM_EINVAL, "n_tokens_total must be a positive multiple of the world size");
+    if (reps == 0) reps = 3;
+    Layer* LA = layer_all >= 0 ? find_layer(c, layer_all) : nullptr;
+    Layer* LC = layer_cols >= 0 ? find_layer(c, layer_cols) : nullptr;
+    if ((layer_all >= 0 && !LA) || (layer_cols >= 0 && !LC)) return fail(c, LUTAMM_ENOLAYER, "no weights loaded for one of the two layers");
+    if (!LA && !LC) return fail(c, LUTAMM_EINVAL, "no candidate: both layers are negative");
+    if (LA && LC && (LA->K != LC->K || LA->N != (size_t)LC->N * G))
+        return fail(c, LUTAMM_EINVAL, "the column layer must hold N / world-size columns of the same operator");
+    const uint32_t K = LA ? LA->K : LC->K;
+    const size_t n_out = (size_t)M * (LA ? LA->N : (size_t)LC->N * G);
+    rep->world = G;
+    for (float& v : rep->ms) v = -1.f;
+
+    // one collective allocation for both operands: the gathered output, then the input rows behind it (when a
+    // rank cannot allocate, every rank learns it there and all leave together)
+    float* d_x = nullptr;
+    void* d_out = nullptr;
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    int rc = LUTAMM_OK;
+    auto cleanup = [&]() {
+        if (e0) cudaEventDestroy(e0);
+        if (e1) cudaEventDestroy(e1);
+        if (d_out) lutamm_shard_free_gathered(c, d_out);
+    };
+    if ((rc = lutamm_shard_alloc_gathered(c, (n_out + (size_t)M * K) * sizeof(float), &d_out))) return rc;
+    d_x = static_cast<float*>(d_out) + n_out;
+    if (cudaMemsetAsync(d_x, 0, (size_t)M * K * sizeof(float), c->stream) != cudaSuccess || cudaEventCreate(&e0) != cudaSuccess ||
+        cudaEventCreate(&e1) != cudaSuccess) {
+        cleanup();
+        return fail(c, LUTAMM_ECUDA, "could not set up the timing run");
+    }
+
+    float* out = static_cast<float*>(d_out);
+    const uint32_t m_loc = M / G;
+    auto call = [&](uint32_t mode) -> int {
+        const float* rows = d_x + (size_t)c->rank * m_loc * K;
+        switch (mode) {
+            case LUTAMM_SHARDING_TOKENS_LOCAL:    return lutamm_amm_token_sharded(c, layer_all, rows, out, M, 0, LUTAMM_FLAG_ASYNC);
+            case LUTAMM_SHARDING_TOKENS_GATHERED: return lutamm_amm_token_sharded(c, layer_all, rows, out, M, 1, LUTAMM_FLAG_ASYNC);
+            case LUTAMM_SHARDING_TOKENS_FUSED:    return lutamm_amm_token_sharded(c, layer_all, rows, out, M, 1, LUTAMM_FLAG_ASYNC | LUTAMM_FLAG_PEER_STORE);
+            case LUTAMM_SHARDING_COLUMNS:         return lutamm_amm_column_sharded(c, layer_cols, d_x, out, M, LUTAMM_SHARD_SEARCH_REPLICATED, LUTAMM_FLAG_ASYNC);
+            case LUTAMM_SHARDING_COLUMNS_SPLIT:   return lutamm_amm_column_sharded(c, layer_cols, d_x, out, M, LUTAMM_SHARD_SEARCH_SPLIT, LUTAMM_FLAG_ASYNC);
+            default:                              return lutamm_amm_column_sharded(c, layer_cols, d_x, out, M, LUTAMM_SHARD_SEARCH_SPLIT, LUTAMM_FLAG_ASYNC | LUTAMM_FLAG_PEER_STORE);
+        }
+    };
+    float mine[LUTAMM_SHARDING_MODES];
+    for (uint32_t mode = 0; mode < LUTAMM_SHARDING_MODES; ++mode) {
+        mine[mode] = -1.f;
+        const bool tokens = mode <= LUTAMM_SHARDING_TOKENS_FUSED;
+        if (tokens ? !LA : !LC) continue;
+        if (G == 1 && (mode == LUTAMM_SHARDING_TOKENS_FUSED || mode == LUTAMM_SHARDING_COLUMNS_FUSED)) continue;  // nothing to fuse
+        const uint64_t unfused_before = c->unfused_exchanges;
+        for (int w = 0; w < 2 && rc == LUTAMM_OK; ++w) rc = call(mode);
+        if (rc == LUTAMM_OK) rc = rank_barrier(c);
+        if (rc != LUTAMM_OK) break;
+        // a plan without a fused kernel ran as kernel + all-gather (on every rank alike: same plan, same shape):
+        // that is the candidate before this one, not a new one
+        if (c->unfused_exchanges != unfused_before) continue;
+        cudaEventRecord(e0, c->stream);
+        for (uint32_t i = 0; i < reps && rc == LUTAMM_OK; ++i) rc = call(mode);
+        cudaEventRecord(e1, c->stream);
+        if (rc != LUTAMM_OK) break;
+        if (cudaStreamSynchronize(c->stream) != cudaSuccess) { rc = fail(c, LUTAMM_ECUDA, "synchronize failed while timing"); break; }
+        if ((rc = check_dev_err(c))) break;
+        float ms = 0.f;
+        cudaEventElapsedTime(&ms, e0, e1);
+        mine[mode] = ms / (float)reps;
+    }
+    if (rc != LUTAMM_OK) { cleanup(); return rc; }
+    // the slowest rank's time per candidate
+    std::vector<float> all((size_t)G * LUTAMM_SHARDING_MODES, -1.f);
+    if (G > 1) {
+        constexpr size_t B = sizeof mine;
+        if ((rc = ensure(c, c->d_build, B * G + 256))) { cleanup(); return rc; }
+        unsigned char* st = static_cast<unsigned char*>(c->d_build.p);
+        cudaMemcpyAsync(st + B * c->rank, mine, B, cudaMemcpyHostToDevice, c->stream);
+        const int e = nccl_api().all_gather(st + B * c->rank, st, B, kNcclUint8, c->comm, c->stream);
+        if (e != kNcclSuccess) { cleanup(); return fail(c, LUTAMM_ECUDA, std::string("ncclAllGather(timings): ") + nccl_api().get_error_string(e)); }
+        if (cudaMemcpyAsync(all.data(), st, B * G, cudaMemcpyDeviceToHost, c->stream) != cudaSuccess || cudaStreamSynchronize(c->stream) != cudaSuccess) {
+            cleanup();
+            return fail(c, LUTAMM_ECUDA, "timing read-back failed");
+        }
+    } else {
+        std::memcpy(all.data(), mine, sizeof mine);
+    }
+    float best_ms = -1.f;
+    rep->best = LUTAMM_SHARDING_TOKENS_GATHERED;
+    for (uint32_t mode = 0; mode < LUTAMM_SHARDING_MODES; ++mode) {
+        float worst = 0.f;
+        for (uint32_t q = 0; q < G; ++q) {
+            const float v = all[(size_t)q * LUTAMM_SHARDING_MODES + mode];
+            if (v < 0.f) { worst = -1.f; break; }
+            worst = std::max(worst, v);
+        }
+        rep->ms[mode] = worst;
+        if (mode != LUTAMM_SHARDING_TOKENS_LOCAL && worst >= 0.f && (best_ms < 0.f || worst < best_ms)) { best_ms = worst; rep->best = mode; }
+    }
+    cleanup();
+    return LUTAMM_OK;
 }
 
 int lutamm_measure_int8_peak(lutamm_ctx* c, double* tops, double* mac_per_clk_sm, double* sm_mhz) {

@@ -93,6 +93,19 @@ def main():
     ctx.amm_token_sharded(1, x[m_lo:m_hi].contiguous(), gfull, M, gather=True, flags=P.FLAG_PEER_STORE)
     assert np.array_equal(gfull[0].cpu().numpy().view(np.uint32), want.view(np.uint32)), (rank, "token-sharded, peer stores")
     ctx.shard_free_gathered(gfull)
+    # ---- which sharding is fastest here: every candidate timed, the same report on every rank
+    ctx.load_weights(0, c.centroid, np.ascontiguousarray(c.lut[:, :, lo:hi]), np.ascontiguousarray(c.bias[lo:hi]), c.scale)
+    rep = ctx.tune_sharding(1, 0, M, reps=2)
+    assert rep["world"] == world and set(rep["ms"]) == set(P.SHARDING_MODES), rep
+    assert all(t is not None and t > 0 for t in rep["ms"].values()), rep          # default plans: every candidate exists
+    assert rep["best"] != "tokens_local" and rep["ms"][rep["best"]] == min(t for n, t in rep["ms"].items() if n != "tokens_local"), rep
+    box = [None] * world
+    dist.all_gather_object(box, rep)
+    assert all(b == box[0] for b in box), box
+    ctx.set_plan(0, variant=P.VARIANT_GATHER)                                       # no fused kernel for this plan
+    rep = ctx.tune_sharding(-1, 0, M, reps=1)
+    assert rep["ms"]["columns_fused"] is None and rep["ms"]["tokens_gathered"] is None and rep["ms"]["columns"] > 0, rep
+    assert rep["best"] in ("columns", "columns_split"), rep
     ctx.shard_finalize()
     ctx.close()
     dist.barrier()

@@ -31,6 +31,14 @@ def test_world_size_one_is_the_plain_operator(ctx):
     assert np.array_equal(y2.cpu().numpy().view(np.uint32), want.view(np.uint32))
     with pytest.raises(P.LutAmmError):
         ctx.amm_column_sharded(20, c.x, y)          # host buffers are refused
+    rep = ctx.tune_sharding(20, 20, 512)            # one GPU: nothing to fuse, every other candidate is timed
+    assert rep["world"] == 1 and rep["ms"]["tokens_fused"] is None and rep["ms"]["columns_fused"] is None
+    assert all(rep["ms"][n] > 0 for n in ("tokens_local", "tokens_gathered", "columns", "columns_split")), rep
+    assert rep["best"] in ("tokens_gathered", "columns", "columns_split")
+    with pytest.raises(P.LutAmmError):
+        ctx.tune_sharding(-1, -1, 512)
+    with pytest.raises(P.LutAmmError):
+        ctx.tune_sharding(20, 99, 512)
     ctx.unload_weights(20)
 
 
