@@ -252,16 +252,18 @@ int lutamm_amm_column_sharded(lutamm_ctx* ctx, int layer_id, const float* input,
  * stores before everybody is done with the previous contents, nobody reads before everybody's kernel is done).
  * Plans the fused kernel is not built for (CUDA-core gather, 64- or 256-wide tiles) fall back to the kernel
  * plus all-gather.  A rank whose allocation fails still takes part in the handle exchange, so every rank
- * returns LUTAMM_ENOMEM together instead of some waiting for it.  The reference's counterpart is the per-DPU read-back of output slabs into one host
- * tensor (src/host/pim_lut_host.cpp:173-203). */
+ * returns LUTAMM_ENOMEM together instead of some waiting for it.  The reference's counterpart is the per-DPU
+ * read-back of output slabs into one host tensor (src/host/pim_lut_host.cpp:173-203). */
 int lutamm_shard_alloc_gathered(lutamm_ctx* ctx, size_t bytes, void** device_ptr);
 int lutamm_shard_free_gathered(lutamm_ctx* ctx, void* device_ptr);
 
-/* Sharding by tokens (the reference's input_parallelism axis): weights replicated, rank r owns rows
- * [r*n/G, (r+1)*n/G) (n_tokens_total % G == 0), nothing is exchanged.  `input_rows` holds this rank's
- * rows.  gather == 0: `output` is this rank's [n/G][N] block.  gather != 0: `output` is the full
- * [n_tokens_total][N] on every rank, written in place by one all-gather - or, with LUTAMM_FLAG_PEER_STORE and
- * a buffer from lutamm_shard_alloc_gathered, by the kernel's own stores as above.  Device buffers only. */
+/* Sharding by tokens (the reference's input_parallelism axis): weights replicated, the ranks own
+ * contiguous near-equal row blocks - n/G rows each, the first n % G ranks one more (C4's 12608 tokens on any
+ * G; a rank left without rows returns at once) - and nothing is exchanged.  `input_rows` holds this rank's
+ * rows.  gather == 0: `output` is this rank's block.  gather != 0 (needs n_tokens_total % G == 0): `output`
+ * is the full [n_tokens_total][N] on every rank, written in place by one all-gather - or, with
+ * LUTAMM_FLAG_PEER_STORE and a buffer from lutamm_shard_alloc_gathered, by the kernel's own stores as above.
+ * Device buffers only. */
 int lutamm_amm_token_sharded(lutamm_ctx* ctx, int layer_id, const float* input_rows, float* output,
                              uint32_t n_tokens_total, uint32_t gather, uint32_t flags);
 

@@ -1121,9 +1121,12 @@ int lutamm_amm_token_sharded(lutamm_ctx* c, int layer_id, const float* input_row
     if (!is_device_ptr(input_rows) || !is_device_ptr(output)) return fail(c, LUTAMM_EINVAL, "the sharded entry points take device buffers");
     if (flags & LUTAMM_FLAG_OUTPUT_TILED) return fail(c, LUTAMM_EINVAL, "tiled output is not offered by the token-sharded call");
     const uint32_t G = (uint32_t)c->world, r = (uint32_t)c->rank;
-    if (M_total % G) return fail(c, LUTAMM_EINVAL, "n_tokens must be a multiple of the world size");
+    // near-equal contiguous row blocks: the first n % G ranks own one row more (an all-gather needs equal blocks)
+    const uint32_t base = M_total / G, extra = M_total % G;
+    if (extra && gather) return fail(c, LUTAMM_EINVAL, "gathering the rows needs n_tokens to be a multiple of the world size");
     if (G > 1 && gather && !c->comm) return fail(c, LUTAMM_EINVAL, "lutamm_shard_init has not been called on this context");
-    const uint32_t m_loc = M_total / G;
+    const uint32_t m_loc = base + (r < extra ? 1u : 0u);
+    if (m_loc == 0) return LUTAMM_OK;  // fewer tokens than ranks: nothing for this one
     int rc;
     if ((rc = ensure(c, c->d_idx, (size_t)m_loc * L->CB))) return rc;
     float* mine = gather ? output + (size_t)r * m_loc * L->N : output;

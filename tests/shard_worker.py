@@ -84,6 +84,17 @@ def main():
     mine = torch.empty(m_hi - m_lo, N, device="cuda")
     ctx.amm_token_sharded(1, x[m_lo:m_hi].contiguous(), mine, M, gather=False)
     assert np.array_equal(mine.cpu().numpy().view(np.uint32), want[m_lo:m_hi].view(np.uint32)), (rank, "token-sharded")
+    # a token count the ranks do not divide: near-equal blocks, the first ranks one row more
+    M_odd = M - 1
+    o_lo, o_hi = shard.token_range(M_odd, rank, world)
+    odd = torch.empty(o_hi - o_lo, N, device="cuda")
+    ctx.amm_token_sharded(1, x[o_lo:o_hi].contiguous(), odd, M_odd, gather=False)
+    assert np.array_equal(odd.cpu().numpy().view(np.uint32), want[o_lo:o_hi].view(np.uint32)), (rank, "token-sharded, uneven")
+    try:
+        ctx.amm_token_sharded(1, x[o_lo:o_hi].contiguous(), odd, M_odd, gather=True)
+        raise AssertionError("gathering uneven blocks must be refused")
+    except P.LutAmmError:
+        pass
     full = torch.full((M, N), float("nan"), device="cuda")
     ctx.amm_token_sharded(1, x[m_lo:m_hi].contiguous(), full, M, gather=True)
     assert np.array_equal(full.cpu().numpy().view(np.uint32), want.view(np.uint32)), (rank, "token-sharded + gather")
