@@ -112,8 +112,17 @@ typedef struct lutamm_plan {
                                  1 = shared memory, 2 = tensor memory (TMEM)             */
     uint32_t umma_sps;        /* tcgen05: 128-byte slabs of the codebook axis a one-hot builder
                                  group takes per turn, 1 or 2 (0 = default; 4 is read as 2)  */
-    uint32_t reserved;
+    uint32_t umma_epilogue;   /* tcgen05: how a finished tile leaves the SM.  LUTAMM_EPILOGUE_TRANSPOSE: through a
+                                 shared-memory transpose and row-contiguous 16-byte stores.  LUTAMM_EPILOGUE_COPY_ENGINE:
+                                 dequantised in the layout tensor memory delivers, staged swizzled and written by tiled
+                                 bulk stores - a third of the instructions, which a CTA with several tiles takes from the
+                                 main loop it runs beside.  0 = the copy engine for launches that give a CTA more
+                                 than one tile.  Launches with split tiles, tiled output, peer stores or the int32
+                                 copy of lutamm_amm_debug always take the transposing form.                  */
 } lutamm_plan;
+#define LUTAMM_EPILOGUE_AUTO        0u
+#define LUTAMM_EPILOGUE_TRANSPOSE   1u
+#define LUTAMM_EPILOGUE_COPY_ENGINE 2u
 
 /* Device times of the last timed call, milliseconds (CUDA events on the context's stream).
  * Mirrors the reference's amm_time accumulators (src/host/utils.h:14-20). */

@@ -23,6 +23,7 @@ VARIANT_AUTO, VARIANT_GATHER, VARIANT_UMMA = 0, 1, 2
 INDEX_U8_ROWMAJOR, INDEX_U16_TILED = 0, 1
 LUT_CANONICAL, LUT_DPU_TILED = 0, 1
 ACT_NONE, ACT_GELU_TANH, ACT_GELU_TANH_F16 = 0, 1, 2
+EPILOGUE_AUTO, EPILOGUE_TRANSPOSE, EPILOGUE_COPY_ENGINE = 0, 1, 2
 
 # every symbol include/lutamm.h declares
 ABI_SYMBOLS = [
@@ -70,11 +71,11 @@ class Plan(ctypes.Structure):
     _fields_ = [("variant", ctypes.c_uint32), ("ccs_tokens", ctypes.c_uint32), ("gather_cfg", ctypes.c_uint32),
                 ("umma_n_tile", ctypes.c_uint32), ("umma_split", ctypes.c_uint32), ("umma_stages", ctypes.c_uint32),
                 ("umma_groups", ctypes.c_uint32), ("umma_operand", ctypes.c_uint32),
-                ("umma_sps", ctypes.c_uint32), ("reserved", ctypes.c_uint32)]
+                ("umma_sps", ctypes.c_uint32), ("umma_epilogue", ctypes.c_uint32)]
 
     def as_dict(self):
         return {k: getattr(self, k) for k in ("variant", "ccs_tokens", "gather_cfg", "umma_n_tile", "umma_split",
-                                              "umma_stages", "umma_groups", "umma_operand", "umma_sps")}
+                                              "umma_stages", "umma_groups", "umma_operand", "umma_sps", "umma_epilogue")}
 
 
 SHARDING_MODES = ("tokens_local", "tokens_gathered", "tokens_fused", "columns", "columns_split", "columns_fused")

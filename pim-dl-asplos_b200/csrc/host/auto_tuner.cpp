@@ -58,6 +58,7 @@ void put_plan(yaml_lite::Doc& doc, const std::string& pre, const GpuPlan& p) {
     put("gpu_variant", p.variant); put("gpu_ccs_tokens", p.ccs_tokens); put("gpu_gather_cfg", p.gather_cfg);
     put("gpu_umma_n_tile", p.umma_n_tile); put("gpu_umma_split", p.umma_split); put("gpu_umma_stages", p.umma_stages);
     put("gpu_umma_groups", p.umma_groups); put("gpu_umma_operand", p.umma_operand); put("gpu_umma_sps", p.umma_sps);
+    put("gpu_umma_epilogue", p.umma_epilogue);
 }
 
 void print_plan(const char* what, const GpuPlan& best) {

@@ -120,7 +120,7 @@ bool parse_amm_configs(AMMParams& p, const std::string& yaml_path, std::string* 
          r.u32(K, "gpu_gather_cfg", &g.gather_cfg, false) && r.u32(K, "gpu_umma_n_tile", &g.umma_n_tile, false) &&
          r.u32(K, "gpu_umma_split", &g.umma_split, false) && r.u32(K, "gpu_umma_stages", &g.umma_stages, false) &&
          r.u32(K, "gpu_umma_groups", &g.umma_groups, false) && r.u32(K, "gpu_umma_operand", &g.umma_operand, false) &&
-         r.u32(K, "gpu_umma_sps", &g.umma_sps, false);
+         r.u32(K, "gpu_umma_sps", &g.umma_sps, false) && r.u32(K, "gpu_umma_epilogue", &g.umma_epilogue, false);
     if (!ok) { *error = yaml_path + ": " + r.err; return false; }
 
     if (verbose) {
@@ -214,7 +214,8 @@ bool parse_linear(Reader& r, const yaml_lite::Doc& doc, const std::string& pre, 
           r.u32(Kp, key("gpu_gather_cfg").c_str(), &g.gather_cfg, false) && r.u32(Kp, key("gpu_umma_n_tile").c_str(), &g.umma_n_tile, false) &&
           r.u32(Kp, key("gpu_umma_split").c_str(), &g.umma_split, false) && r.u32(Kp, key("gpu_umma_stages").c_str(), &g.umma_stages, false) &&
           r.u32(Kp, key("gpu_umma_groups").c_str(), &g.umma_groups, false) && r.u32(Kp, key("gpu_umma_operand").c_str(), &g.umma_operand, false) &&
-          r.u32(Kp, key("gpu_umma_sps").c_str(), &g.umma_sps, false))) {
+          r.u32(Kp, key("gpu_umma_sps").c_str(), &g.umma_sps, false) &&
+          r.u32(Kp, key("gpu_umma_epilogue").c_str(), &g.umma_epilogue, false))) {
         *why = r.err;
         return false;
     }

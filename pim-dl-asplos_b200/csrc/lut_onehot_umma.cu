@@ -55,6 +55,7 @@ constexpr uint32_t kMaxASlots = 8;    // one-hot slabs in flight (tensor memory:
 constexpr uint32_t kMaxBSlots = 16;   // LUT slabs in flight (shared memory)
 constexpr uint32_t kNumBarriers = 2 * kMaxASlots + 2 * kMaxBSlots + 4;
 constexpr uint32_t kStageWarpBytes = 32 * 128;           // epilogue transpose buffer per warp
+constexpr uint32_t kBiasWarpBytes = 256 * 4;             // a tile's bias values, one copy per epilogue warp (store-by-copy-engine epilogue)
 // One-hot table: row e (0..15) holds the 16 bytes "byte e = 1", row 16 holds zeros; a row is 128
 // bytes = eight copies, and lane l reads copy l % 8, so a 16-byte load is free of bank conflicts
 // whatever indices the lanes of a warp hold.
@@ -101,6 +102,7 @@ __device__ __forceinline__ uint32_t div_magic(uint32_t x, uint32_t magic) { retu
 struct Item {
     uint32_t m0, n0, slab_begin, nslab, tile, z;
 };
+__device__ __forceinline__ uint32_t rsw_of(uint32_t row) { return row & 7u; }
 __device__ __forceinline__ Item decode_item(const UmmaParams& p, uint32_t item, uint32_t n_tile) {
     Item it;
     const uint32_t z = item % p.split, tile = item / p.split;
@@ -114,9 +116,9 @@ __device__ __forceinline__ Item decode_item(const UmmaParams& p, uint32_t item, 
     return it;
 }
 
-template <uint32_t N_TILE, bool A_TMEM, uint32_t SPS, bool PEER = false>
+template <uint32_t N_TILE, bool A_TMEM, uint32_t SPS, bool PEER = false, bool EPI_TMA = false>
 __global__ void __launch_bounds__(kMaxThreads, 1)
-lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const UmmaParams p) {
+lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const UmmaParams p, const __grid_constant__ CUtensorMap out_map) {
     constexpr uint32_t kBBytes = N_TILE * kSlabK;
     constexpr uint32_t kIdesc = umma_idesc_i8(kMTile, N_TILE, /*a_signed=*/1, /*b_signed=*/1);
     // Tensor memory: two accumulators of N_TILE columns; with A_TMEM also the ring of one-hot
@@ -138,6 +140,7 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
     unsigned char* s_tab = s_stage + kEpiWarps * kStageWarpBytes;  // one-hot table, 128-byte aligned
     uint64_t* s_bar = reinterpret_cast<uint64_t*>(s_tab + kOneHotTabBytes);
     uint32_t* s_misc = reinterpret_cast<uint32_t*>(s_bar + kNumBarriers);  // tmem base, abort, last
+    float* s_bias = reinterpret_cast<float*>(s_misc + 4);                  // [4][256] (EPI_TMA only)
     volatile uint32_t* s_abort = s_misc + 1;
 
     const uint32_t a_full0 = smem_u32(s_bar), a_empty0 = a_full0 + 8 * kMaxASlots, b_full0 = a_empty0 + 8 * kMaxASlots,
@@ -420,6 +423,69 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
         const uint32_t et = threadIdx.x - kFirstEpiWarp * 32;
         const float lbcb = lut_bias_times_cb(a.lut_bias, a.CB);
         unsigned char* stg = s_stage + (warp - kFirstEpiWarp) * kStageWarpBytes;
+        if constexpr (EPI_TMA) {
+            // The tile leaves through the copy engine: each thread dequantises the 32 columns of its own row in
+            // the layout tcgen05.ld delivers, writes them as eight 16-byte shared-memory stores (128-byte swizzle,
+            // conflict free) and one lane hands the 32 x 32 block to a tiled store, which also clips rows past M
+            // and columns past N.  A third of the instructions of the transposing path below, and no load/store-unit
+            // traffic for the global stores: what the epilogue issues is taken from the builders' latency chain.
+            // (Launches with split tiles, tiled output, an int32 copy or peer stores use the path below.)
+            float* bw = s_bias + (warp - kFirstEpiWarp) * (kBiasWarpBytes / 4);
+            if (lane == 0) tma_prefetch_desc(&out_map);
+            uint32_t t = 0;
+            bool ok = true;
+            for (uint32_t item = blockIdx.x; item < n_items; item += gridDim.x, ++t) {
+                const Item it = decode_item(p, item, N_TILE);
+                const uint32_t ab = t & 1, aph = (t >> 1) & 1;
+                __syncwarp();  // the previous item's reads of bw are done
+#pragma unroll
+                for (uint32_t c = 0; c < N_TILE / 32; ++c) {
+                    const uint32_t n = it.n0 + c * 32 + lane;
+                    bw[c * 32 + lane] = n < a.N ? __ldg(a.bias + n) : 0.f;
+                }
+                uint32_t w_ok = 1;
+                if (lane == 0) w_ok = (ok && mbar_wait<256>(acc_full0 + 8 * ab, aph, s_abort)) ? 1u : 0u;
+                ok = __shfl_sync(0xffffffffu, w_ok, 0) != 0;
+                if (!ok) continue;
+                tc_fence_after_sync();
+                for (uint32_t c = 0; c < N_TILE / 32; ++c) {
+                    uint32_t v[32];
+                    tmem_ld_32x32b_x32(tmem_base + ((quad * 32u) << 16) + ab * N_TILE + c * 32u, v);
+                    tmem_ld_wait();
+                    {   // leave the columns at zero for the next item's accumulating MMAs
+                        const uint32_t zero[32] = {};
+                        tmem_st_32x32b_x32(tmem_base + ((quad * 32u) << 16) + ab * N_TILE + c * 32u, zero);
+                    }
+                    if (c == N_TILE / 32 - 1) {  // accumulator fully read and cleared: hand the buffer back
+                        tmem_st_wait();
+                        tc_fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(acc_empty0 + 8 * ab);
+                    }
+                    if (it.n0 + c * 32 >= a.N || it.m0 + quad * 32 >= a.M) continue;  // a block wholly past N or M (warp-uniform)
+                    // the previous block's copy has read the staging buffer
+                    if (lane == 0) tma_store_wait_read();
+                    __syncwarp();
+#pragma unroll
+                    for (uint32_t q = 0; q < 8; ++q) {
+                        const float4 b4 = *reinterpret_cast<const float4*>(bw + c * 32 + 4 * q);
+                        float4 o = make_float4(dequant_one((int32_t)v[4 * q], a.scale, lbcb, b4.x), dequant_one((int32_t)v[4 * q + 1], a.scale, lbcb, b4.y),
+                                               dequant_one((int32_t)v[4 * q + 2], a.scale, lbcb, b4.z), dequant_one((int32_t)v[4 * q + 3], a.scale, lbcb, b4.w));
+                        if (a.act) { o.x = activate_one(o.x, a.act); o.y = activate_one(o.y, a.act); o.z = activate_one(o.z, a.act); o.w = activate_one(o.w, a.act); }
+                        *reinterpret_cast<float4*>(stg + lane * 128 + ((q ^ rsw_of(lane)) << 4)) = o;
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_2d(&out_map, smem_u32(stg), (int32_t)(it.n0 + c * 32), (int32_t)(it.m0 + quad * 32));
+                        tma_store_commit();
+                    }
+                }
+            }
+            if (lane == 0) tma_store_wait_all();  // shared memory and the output are settled before the CTA leaves
+            __syncwarp();
+            tc_fence_before_sync();
+        } else {
         const uint32_t rsw = lane & 7u;
         const uint32_t ch = lane & 7u, rsub = lane >> 3;  // store phase: 16-byte column group, row within a pass
         uint32_t t = 0;
@@ -618,6 +684,7 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
             }
         }
         tc_fence_before_sync();
+        }
     }
 
     // ---------------- tear-down (also the way out after a wait that ran out)
@@ -640,14 +707,14 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
 
 size_t umma_smem_bytes(uint32_t n_tile, uint32_t a_slots, uint32_t b_slots, bool a_tmem) {
     return (size_t)(a_tmem ? 0 : a_slots) * kABytes + (size_t)b_slots * n_tile * kSlabK + kEpiWarps * kStageWarpBytes +
-           kOneHotTabBytes + kNumBarriers * 8 + 16 + 1024;
+           kOneHotTabBytes + kNumBarriers * 8 + 16 + kEpiWarps * kBiasWarpBytes + 1024;
 }
 constexpr size_t kSmemLimit = 227 * 1024;
 constexpr size_t kSmemOneCtaPerSm = 116 * 1024;  // of 228 KiB per SM
 
-template <uint32_t N_TILE, bool A_TMEM, uint32_t SPS, bool PEER = false>
-cudaError_t run(const CUtensorMap& map, const UmmaParams& p, uint32_t grid, size_t smem, cudaStream_t s) {
-    auto k = lut_onehot_umma_kernel<N_TILE, A_TMEM, SPS, PEER>;
+template <uint32_t N_TILE, bool A_TMEM, uint32_t SPS, bool PEER = false, bool EPI_TMA = false>
+cudaError_t run(const CUtensorMap& map, const UmmaParams& p, uint32_t grid, size_t smem, cudaStream_t s, const CUtensorMap* out_map = nullptr) {
+    auto k = lut_onehot_umma_kernel<N_TILE, A_TMEM, SPS, PEER, EPI_TMA>;
     // Never two of these CTAs on one SM: the second would sit in tcgen05.alloc until the first has
     // freed its tensor memory, and with split tiles the first may be waiting for the second's slice.
     // The grid is at most one CTA per SM, but while the preceding kernel still holds some SMs
@@ -666,7 +733,7 @@ cudaError_t run(const CUtensorMap& map, const UmmaParams& p, uint32_t grid, size
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, k, map, p);
+    return cudaLaunchKernelEx(&cfg, k, map, p, out_map ? *out_map : map);  // (the third argument is read by EPI_TMA instances only)
 }
 
 // Ring depths.  One-hot slots: an even number (two warps issue alternate slabs); in tensor memory what the
@@ -758,6 +825,7 @@ void umma_default_plan(uint32_t M, uint32_t CB, uint32_t CT, uint32_t N, int sm_
     p->groups = 0;
     p->sps = sps;  // 0: chosen at launch from the ring depth
     p->max_ctas = (uint32_t)sm_count;
+    p->epilogue = 0;
 }
 
 cudaError_t umma_make_tmap(CUtensorMap* out, const int8_t* lut_t, uint32_t CB, uint32_t CT, uint32_t N,
@@ -776,6 +844,20 @@ cudaError_t umma_make_tmap(CUtensorMap* out, const int8_t* lut_t, uint32_t CB, u
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) { *why = "cuTensorMapEncodeTiled failed for the transposed LUT map"; return cudaErrorInvalidValue; }
+    return cudaSuccess;
+}
+
+// fp32 [M][N] row-major output as 32 x 32 blocks with the 128-byte swizzle the epilogue stages them in
+static cudaError_t make_out_tmap(CUtensorMap* out, float* base, uint32_t M, uint32_t N, const char** why) {
+    EncodeTiledFn enc = get_encode_tiled();
+    if (!enc) { *why = "cuTensorMapEncodeTiled is not available from this driver"; return cudaErrorNotSupported; }
+    cuuint64_t dims[2] = {N, M};
+    cuuint64_t strides[1] = {(cuuint64_t)N * 4};
+    cuuint32_t box[2] = {32, 32};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { *why = "cuTensorMapEncodeTiled failed for the output map"; return cudaErrorInvalidValue; }
     return cudaSuccess;
 }
 
@@ -835,6 +917,19 @@ cudaError_t launch_umma(const LutArgs& a, const CUtensorMap& lut_t_map, const Um
         if (plan.n_tile == 128 && a_tmem && sps == 1) return run<128, true, 1, true>(lut_t_map, p, grid, smem, s);
         *why = "tcgen05 variant: peer stores are built for 128- and 192-wide tiles with the one-hot operand in tensor memory";
         return cudaErrorNotSupported;
+    }
+    {
+        const bool eligible = !a.n_peers && split == 1 && !a.layout.tiled && !a.acc_out && a_tmem && sps == 1 &&
+                              (plan.n_tile == 192 || plan.n_tile == 128) && (reinterpret_cast<uintptr_t>(a.out) & 15u) == 0;
+        // a CTA with several tiles runs the epilogue beside the next tile's main loop, where every instruction it
+        // issues lengthens the builders' latency chain: there the copy-engine form pays (BERT-large step -3 %)
+        if (eligible && (plan.epilogue == 2 || (plan.epilogue == 0 && items > grid))) {
+            CUtensorMap om;
+            cudaError_t e = make_out_tmap(&om, a.out, a.M, a.N, why);
+            if (e != cudaSuccess) return e;
+            if (plan.n_tile == 192) return run<192, true, 1, false, true>(lut_t_map, p, grid, smem, s, &om);
+            return run<128, true, 1, false, true>(lut_t_map, p, grid, smem, s, &om);
+        }
     }
 #define LUTAMM_UMMA_CASE(NT, TM, SP) \
     if (plan.n_tile == NT && a_tmem == TM && sps == SP) return run<NT, TM, SP>(lut_t_map, p, grid, smem, s);

@@ -224,6 +224,7 @@ int run_lut(lutamm_ctx* c, Layer& L, const uint8_t* d_idx, float* d_out, int32_t
         up.stages = plan.umma_stages;
         up.groups = plan.umma_groups;
         if (plan.umma_sps) up.sps = plan.umma_sps;
+        up.epilogue = plan.umma_epilogue;
         if (!umma_tile_ok(up.n_tile, a_tmem))
             return fail(c, LUTAMM_EINVAL, "umma_n_tile must be 64, 128 or 256 with the one-hot operand in shared memory, "
                                           "64, 128, 160 or 192 with it in tensor memory");
@@ -720,6 +721,7 @@ int lutamm_set_plan(lutamm_ctx* c, int layer_id, const lutamm_plan* plan) {
                                       "0, 64, 128, 160 or 192 with it in tensor memory");
     if (plan->umma_sps != 0 && plan->umma_sps != 1 && plan->umma_sps != 2 && plan->umma_sps != 4)
         return fail(c, LUTAMM_EINVAL, "umma_sps must be 0, 1, 2 or 4");
+    if (plan->umma_epilogue > LUTAMM_EPILOGUE_COPY_ENGINE) return fail(c, LUTAMM_EINVAL, "unknown umma_epilogue");
     if (plan->variant == LUTAMM_VARIANT_UMMA && !umma_supported(L->CB, L->CT, L->N))
         return fail(c, LUTAMM_EUNSUPPORTED, "tcgen05 variant does not cover this shape");
     L->plan = *plan;

@@ -10,6 +10,7 @@ mapping space is the execution plan of the library (lutamm_plan), so the same ex
   operand-tile   where the one-hot operand lives (tensor / shared memory) x tile width      (tcgen05 kernel)
   split-ring     split of the codebook axis x depth of the LUT ring                         (tcgen05 kernel)
   builders       one-hot builder groups x tile width                                        (tcgen05 kernel)
+  epilogue       how finished tiles leave the SM (transposing stores / copy engine) x width (tcgen05 kernel)
   gather         tile configurations of the CUDA-core gather kernel
   global         all of the above in one table, with the tuner's pick, the measured best and the worst marked
 
@@ -30,7 +31,7 @@ PKG = os.path.dirname(HERE)
 sys.path.insert(0, os.path.dirname(PKG))
 
 SHAPE = dict(n=32768, K=1024, N=4096, CB=256, CT=16)   # search-space-illustration/configs/*/*.yaml
-EXPERIMENTS = ("operand-tile", "split-ring", "builders", "gather", "global")
+EXPERIMENTS = ("operand-tile", "split-ring", "builders", "epilogue", "gather", "global")
 
 
 def points(experiment: str):
@@ -45,6 +46,9 @@ def points(experiment: str):
     if experiment == "builders":
         return [(f"{g}-{nt}", dict(variant=U, umma_operand=2, umma_n_tile=nt, umma_split=1, umma_groups=g))
                 for nt in (128, 192) for g in (1, 2, 3, 4)]
+    if experiment == "epilogue":   # 1 = transposing stores, 2 = tiled bulk stores by the copy engine
+        return [(f"{ep}-{nt}", dict(variant=U, umma_operand=2, umma_n_tile=nt, umma_split=1, umma_epilogue=ep))
+                for nt in (128, 192) for ep in (1, 2)]
     if experiment == "gather":
         return [(f"{cfg}", dict(variant=G, gather_cfg=cfg)) for cfg in range(5)]
     if experiment == "global":
@@ -126,7 +130,7 @@ def run_experiment(bench, experiment: str, out_dir: str):
         best, worst = min(ok, key=lambda r: r["amm_time_s"]), max(ok, key=lambda r: r["amm_time_s"])
         rows.append(dict(experiment=experiment, point="tuner pick", amm_time_s=t_pick, speedup_over_default=base / t_pick,
                          **{k: v for k, v in pick.items() if k in ("variant", "gather_cfg", "umma_n_tile", "umma_split", "umma_stages",
-                                                                   "umma_groups", "umma_operand")}))
+                                                                   "umma_groups", "umma_operand", "umma_epilogue")}))
         print(f"best mapping in the tuner: {t_pick:.6f} s; best in real performance: {best['point']} {best['amm_time_s']:.6f} s; "
               f"worst: {worst['point']} {worst['amm_time_s']:.6f} s; default plan {base:.6f} s")
     write_csv(os.path.join(out_dir, experiment + ".csv"), rows)

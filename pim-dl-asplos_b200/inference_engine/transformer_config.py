@@ -3,7 +3,7 @@ parsed there by parse_transformer_configs(), src/host/parser.cpp:89-413)."""
 import yaml
 
 LINEARS = ("qkv", "o", "ffn1", "ffn2")
-PLAN_KEYS = ("variant", "ccs_tokens", "gather_cfg", "umma_n_tile", "umma_split", "umma_stages", "umma_groups", "umma_operand", "umma_sps")
+PLAN_KEYS = ("variant", "ccs_tokens", "gather_cfg", "umma_n_tile", "umma_split", "umma_stages", "umma_groups", "umma_operand", "umma_sps", "umma_epilogue")
 
 
 def load(path):

@@ -28,6 +28,9 @@ def variants_for(CT, N, CB=16):
               ("umma_ts128s", dict(variant=U, umma_operand=2, umma_n_tile=128, umma_split=3, umma_sps=4)),
               ("umma_ts64", dict(variant=U, umma_operand=2, umma_n_tile=64, umma_split=1, umma_groups=2, umma_sps=4)),
               ("umma_ts192_1", dict(variant=U, umma_operand=2, umma_n_tile=192, umma_split=2, umma_sps=1, umma_groups=3)),
+              ("umma_ts192_ce", dict(variant=U, umma_operand=2, umma_n_tile=192, umma_split=1, umma_epilogue=P.EPILOGUE_COPY_ENGINE)),
+              ("umma_ts128_ce", dict(variant=U, umma_operand=2, umma_n_tile=128, umma_split=1, umma_epilogue=P.EPILOGUE_COPY_ENGINE)),
+              ("umma_ts192_tr", dict(variant=U, umma_operand=2, umma_n_tile=192, umma_split=1, umma_epilogue=P.EPILOGUE_TRANSPOSE)),
               ("umma_auto", dict(variant=U))]
     return v
 
@@ -319,6 +322,9 @@ def test_fused_activation(ctx, M, K, N, v, CT):
             if first is None:
                 first = g_out
             assert np.array_equal(g_out.view(np.uint32), first.view(np.uint32)), f"{name}: plans disagree"
+            y_prod = np.zeros_like(g_out)      # the production call (no int32 copy): the copy-engine epilogue where the plan asks for it
+            ctx.amm_host(3, c.x, y_prod)
+            assert np.array_equal(y_prod.view(np.uint32), first.view(np.uint32)), f"{name}: amm_host != amm_debug"
     ctx.set_activation(3, P.ACT_NONE)
     ctx.set_plan(3, variant=P.VARIANT_AUTO)
     y = np.zeros_like(out)

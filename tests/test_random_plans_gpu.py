@@ -33,7 +33,7 @@ def test_random_shapes_and_plans(ctx, seed):
             tiles = {0: [0], 1: [0, 64, 128, 256], 2: [0, 64, 128, 160, 192]}[op]
             plan = dict(variant=P.VARIANT_UMMA, umma_operand=op, umma_n_tile=int(rng.choice(tiles)),
                         umma_split=int(rng.choice([0, 0, 1, 2, 3, 4, 5, 7, 12])), umma_groups=int(rng.integers(0, 5)),
-                        umma_sps=int(rng.choice([0, 1, 2, 4])),
+                        umma_sps=int(rng.choice([0, 1, 2, 4])), umma_epilogue=int(rng.choice([0, 1, 2, 2])),
                         umma_stages=int(rng.choice([0, 0, 2, 3, 4, 5, 7, 9, 12, 13, 16])))
             ctx.set_plan(5, **plan)
             for _rep in range(2):
@@ -42,4 +42,7 @@ def test_random_shapes_and_plans(ctx, seed):
                 assert np.array_equal(g_idx, idx.astype(np.uint8)), where
                 assert np.array_equal(g_acc, acc), where
                 assert np.array_equal(g_out.view(np.uint32), out.view(np.uint32)), where
+            y = np.zeros_like(out)                 # the production call: no int32 copy, so the plan's epilogue form runs
+            ctx.amm_host(5, c.x, y)
+            assert np.array_equal(y.view(np.uint32), out.view(np.uint32)), "amm_host: " + where
         ctx.unload_weights(5)
