@@ -116,9 +116,9 @@ typedef struct lutamm_plan {
                                  shared-memory transpose and row-contiguous 16-byte stores.  LUTAMM_EPILOGUE_COPY_ENGINE:
                                  dequantised in the layout tensor memory delivers, staged swizzled and written by tiled
                                  bulk stores - a third of the instructions, which a CTA with several tiles takes from the
-                                 main loop it runs beside.  0 = the copy engine for launches that give a CTA more
-                                 than one tile.  Launches with split tiles, tiled output, peer stores or the int32
-                                 copy of lutamm_amm_debug always take the transposing form.                  */
+                                 main loop it runs beside.  0 = the copy engine wherever the launch admits it: launches
+                                 with split tiles, tiled output, peer stores, 64- / 160- / 256-wide tiles or the
+                                 int32 copy of lutamm_amm_debug always take the transposing form.            */
 } lutamm_plan;
 #define LUTAMM_EPILOGUE_AUTO        0u
 #define LUTAMM_EPILOGUE_TRANSPOSE   1u

@@ -64,7 +64,7 @@ struct UmmaPlan {
     uint32_t groups;    // one-hot builder groups of four warps (0 = default)
     uint32_t sps;       // 128-byte slabs a one-hot builder group takes per turn: 1 or 2 (0 = by ring depth)
     uint32_t max_ctas;  // persistent grid size cap: the SM count
-    uint32_t epilogue;  // 0 = by tiles per CTA, 1 = transposing stores, 2 = tiled bulk stores where the launch admits them
+    uint32_t epilogue;  // 1 = transposing stores; 0 / 2 = tiled bulk stores where the launch admits them
 };
 bool umma_supported(uint32_t CB, uint32_t CT, uint32_t N);
 bool umma_tile_ok(uint32_t n_tile, bool a_tmem);

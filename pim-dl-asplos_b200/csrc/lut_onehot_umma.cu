@@ -921,9 +921,10 @@ cudaError_t launch_umma(const LutArgs& a, const CUtensorMap& lut_t_map, const Um
     {
         const bool eligible = !a.n_peers && split == 1 && !a.layout.tiled && !a.acc_out && a_tmem && sps == 1 &&
                               (plan.n_tile == 192 || plan.n_tile == 128) && (reinterpret_cast<uintptr_t>(a.out) & 15u) == 0;
-        // a CTA with several tiles runs the epilogue beside the next tile's main loop, where every instruction it
-        // issues lengthens the builders' latency chain: there the copy-engine form pays (BERT-large step -3 %)
-        if (eligible && (plan.epilogue == 2 || (plan.epilogue == 0 && items > grid))) {
+        // A CTA with several tiles runs the epilogue beside the next tile's main loop, where every instruction it
+        // issues lengthens the builders' latency chain: there the copy-engine form pays most (BERT-large step
+        // -3 %); after a CTA's only tile it still shortens the tail a little (BERT-base step -1 %).
+        if (eligible && plan.epilogue != 1) {
             CUtensorMap om;
             cudaError_t e = make_out_tmap(&om, a.out, a.M, a.N, why);
             if (e != cudaSuccess) return e;
