@@ -109,9 +109,9 @@ def test_tuned_plans_round_trip(tmp_path):
     import transformer_config
     _, raw = transformer_config.load(os.path.join(CFG, "bert_base_layer.yaml"))
     out = tmp_path / "t.yaml"
-    transformer_config.save_with_plans(raw, {"ffn1": {"variant": 2, "umma_n_tile": 192, "umma_operand": 2}}, str(out))
+    transformer_config.save_with_plans(raw, {"ffn1": {"variant": 2, "umma_n_tile": 192, "umma_operand": 2, "umma_epilogue": 1}}, str(out))
     cfg, _ = transformer_config.load(str(out))
-    assert cfg["plans"] == {"ffn1": {"variant": 2, "umma_n_tile": 192, "umma_operand": 2}}
+    assert cfg["plans"] == {"ffn1": {"variant": 2, "umma_n_tile": 192, "umma_operand": 2, "umma_epilogue": 1}}
 
 
 def test_sensitivity_sweep_configs(tmp_path):
@@ -198,6 +198,7 @@ def test_cpp_transformer_parser_reads_the_reference_schema(tmp_path):
     (("head_dim: 64", "head_dim: 48"), "head_dim * head_num != token_dim"),
     (("  o_input_parallelism: 8", "  o_input_parallelism: 16"), "o: input_parallelism * lut_parallelism != dpu_num"),
     (("  ffn1_cb_load_tile_size: 32", "  ffn1_cb_load_tile_size: 5"), "ffn1: cb_mtile_size % cb_load_tile_size"),
+    (("  o_loop_order: 0", "  o_loop_order: 0\n  o_gpu_umma_epilogue: copy"), "kernel_params.o_gpu_umma_epilogue: not an unsigned integer"),
     (("  qkv_num_centroid: 16\n", ""), "missing kernel_params.qkv_num_centroid"),
     (("  seq_len: 64\n", ""), "missing network_params.seq_len"),
 ])
