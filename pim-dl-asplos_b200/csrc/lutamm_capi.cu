@@ -62,6 +62,12 @@ struct Buf {
 
 }  // namespace
 
+// Staging slots of the host-buffer pipeline.  With two, a slab's kernels wait for the copy-out of the slab before
+// last, and copy-outs of very different sizes (3 to 12 MB per linear of a BERT-base layer) leave the link idle in
+// between; a third decouples them (that layer's step through host buffers 0.69-0.74 -> 0.64 ms, BERT-large 6.6 ->
+// 6.2 ms on the same box); a fourth adds nothing.
+constexpr int kHostSlots = 3;
+
 struct lutamm_ctx {
     int device = 0;
     int sm_count = 148;
@@ -70,10 +76,10 @@ struct lutamm_ctx {
     cudaStream_t stream = nullptr;
     std::map<int, Layer> layers;
     Buf d_in, d_out, d_idx, d_idx16, d_acc_dbg, d_acc_scratch, d_counters, d_build;
-    // host-buffer pipeline: copy-in and copy-out streams, two staging slots
+    // host-buffer pipeline: copy-in and copy-out streams, kHostSlots staging slots
     cudaStream_t s_in = nullptr, s_out = nullptr;
-    Buf p_in[2], p_out[2];
-    cudaEvent_t ev_in[2] = {}, ev_comp[2] = {}, ev_out[2] = {};
+    Buf p_in[kHostSlots], p_out[kHostSlots];
+    cudaEvent_t ev_in[kHostSlots] = {}, ev_comp[kHostSlots] = {}, ev_out[kHostSlots] = {};
     uint32_t slot = 0;
     uint32_t* d_err = nullptr;
     uint32_t* h_err = nullptr;  // pinned
@@ -317,7 +323,7 @@ int check_dev_err(lutamm_ctx* c) {
 
 // Host buffers on both sides: a three-stream pipeline.  Rows go through in chunks; chunk j is
 // copied in on s_in, computed on the context's stream and copied out on s_out, each stage
-// ordered by events, with two staging slots so that the copy-in of the next chunk (or of the
+// ordered by events, with three staging slots so that the copy-in of the next chunk (or of the
 // next call, with LUTAMM_FLAG_ASYNC), the kernels and the copy-out of the previous one overlap
 // and both directions of the host link are busy at once.  The reference's counterpart are the
 // serial host<->DPU transfers around dpu_launch (pim_lut_host.cpp:143-181).
@@ -331,13 +337,14 @@ int amm_host_pipelined(lutamm_ctx* c, Layer& L, const float* input, float* outpu
     if ((flags & LUTAMM_FLAG_OUTPUT_TILED) || rows >= M) { rows = M; }
     int r;
     if ((r = ensure(c, c->d_idx, (size_t)rows * L.CB))) return r;
-    for (int k = 0; k < 2; ++k) {
+    constexpr uint32_t n_slots = kHostSlots;
+    for (uint32_t k = 0; k < n_slots; ++k) {
         if ((r = ensure(c, c->p_in[k], (size_t)rows * L.K * sizeof(float)))) return r;
         if ((r = ensure(c, c->p_out[k], (size_t)rows * L.N * sizeof(float)))) return r;
     }
     for (uint32_t m0 = 0; m0 < M; m0 += rows) {
         const uint32_t m = std::min(rows, M - m0);
-        const uint32_t k = c->slot++ & 1u;
+        const uint32_t k = c->slot++ % n_slots;
         float* d_x = static_cast<float*>(c->p_in[k].p);
         float* d_y = static_cast<float*>(c->p_out[k].p);
         CU_TRY(c, cudaStreamWaitEvent(c->s_in, c->ev_comp[k], 0));   // kernels that read this slot are done
@@ -463,7 +470,7 @@ int lutamm_create(lutamm_ctx** out, int device) {
     for (auto& ev : c->ev) cudaEventCreate(&ev);
     cudaStreamCreateWithFlags(&c->s_in, cudaStreamNonBlocking);
     cudaStreamCreateWithFlags(&c->s_out, cudaStreamNonBlocking);
-    for (int k = 0; k < 2; ++k) {
+    for (int k = 0; k < kHostSlots; ++k) {
         cudaEventCreateWithFlags(&c->ev_in[k], cudaEventDisableTiming);
         cudaEventCreateWithFlags(&c->ev_comp[k], cudaEventDisableTiming);
         cudaEventCreateWithFlags(&c->ev_out[k], cudaEventDisableTiming);
@@ -488,7 +495,7 @@ int lutamm_destroy(lutamm_ctx* c) {
     if (c->comm && nccl_api().ok) nccl_api().comm_destroy(c->comm);
     c->comm = nullptr;
     for (auto& kv : c->layers) free_layer(kv.second);
-    for (int k = 0; k < 2; ++k) {
+    for (int k = 0; k < kHostSlots; ++k) {
         cudaFree(c->p_in[k].p); cudaFree(c->p_out[k].p);
         if (c->ev_in[k]) cudaEventDestroy(c->ev_in[k]);
         if (c->ev_comp[k]) cudaEventDestroy(c->ev_comp[k]);
