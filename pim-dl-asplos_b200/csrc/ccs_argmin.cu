@@ -70,21 +70,18 @@ ccs_reg_kernel(const float* __restrict__ x, const float* __restrict__ cent, void
     // set-up, tensor-memory allocation, the first LUT tiles - while the search runs; it
     // waits for this grid to finish before it touches the indices.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    // This kernel is itself launched as a programmatic dependent of whatever precedes it in the stream
-    // (so that its launch latency overlaps that kernel's tail): everything it reads or overwrites - the
-    // activations, the index buffer the previous LUT kernel may still be reading - comes after this wait,
-    // which returns once the preceding grid has completed and its writes are visible.
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    // This kernel is itself launched as a programmatic dependent of whatever precedes it in the stream, so
+    // that its launch latency and the staging of its centroids - weights, which no preceding kernel writes -
+    // overlap that kernel's tail.  Everything else it reads or overwrites - the activations, the index buffer
+    // the previous LUT kernel may still be reading - comes after griddepcontrol.wait below, which returns
+    // once the preceding grid has completed and its writes are visible.
     const uint32_t cb = blockIdx.x * kRegThreads + threadIdx.x;
     const bool active = cb < CB;
     const uint32_t m0 = blockIdx.y * tokens_per_cta;
     const uint32_t m1 = min(M, m0 + tokens_per_cta);
 
-    // first batch of activations before the centroids, so both round trips overlap
     float xs[kTok][V];
     const float* xp = x + (size_t)(active ? cb : 0) * V;
-#pragma unroll
-    for (int t = 0; t < kTok; ++t) load_x<V>(xp + (size_t)min(m0 + t, M - 1) * K, xs[t]);
 
     // Centroids are kept negated (the sign is flipped while they are staged) so that x - c becomes x + (-c): the same IEEE result, and
     // for even V two dimensions go through one packed add.rn.f32x2 / mul.rn.f32x2 (each lane
@@ -114,6 +111,10 @@ ccs_reg_kernel(const float* __restrict__ x, const float* __restrict__ cent, void
             s_cent[r * kPitch + i] = -__ldg(gp + e);
         }
     }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    // first batch of activations: in flight while the CTA waits at the barrier for the centroids
+#pragma unroll
+    for (int t = 0; t < kTok; ++t) load_x<V>(xp + (size_t)min(m0 + t, M - 1) * K, xs[t]);
     __syncthreads();
     if (!active) return;
     float nc[kCentInSmem ? 1 : CT][V];

@@ -73,6 +73,7 @@ struct UmmaParams {
     uint32_t tiles_m, tiles_n;
     uint32_t log2_ct;
     uint32_t groups;         // A-builder groups (1..4); a_slots % (groups * slabs per turn) == 0
+    uint32_t early_trigger;  // 1: let the next kernel of the stream start once this CTA's main loops are done
     int32_t* acc_scratch;    // [split][M][N] int32 partial sums (split > 1); needs no initialisation
     uint32_t* tile_counters;
     uint32_t* dev_err;
@@ -212,6 +213,7 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
             }
         }
         __syncwarp();
+        if (p.early_trigger) pdl_launch_dependents();
     } else if (warp < kFirstAgenWarp) {
         // ---------------- MMA issuers: two warps, slab x of the CTA's sequence goes to warp x % 2.
         // A slab's turn (barrier probes, fence, election, four tcgen05.mma of 32 bytes of K each, one
@@ -283,6 +285,7 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
             }
         }
         __syncwarp();
+        if (p.early_trigger) pdl_launch_dependents();
     } else if (warp < kFirstEpiWarp) {
         // ---------------- one-hot A builders: groups of 4 warps; group k owns every
         // kAgenGroups-th slab of the CTA's slab sequence, one tile row per thread, so the
@@ -416,6 +419,7 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
             ga += it.nslab;
             qb += (it.nslab + kBatch - 1) / kBatch;
         }
+        if (p.early_trigger) pdl_launch_dependents();
     } else {
         // ---------------- epilogue: four warps, each on the TMEM lane quadrant (warp % 4) it may read
         pdl_wait_prior_grid();
@@ -437,6 +441,7 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
             for (uint32_t item = blockIdx.x; item < n_items; item += gridDim.x, ++t) {
                 const Item it = decode_item(p, item, N_TILE);
                 const uint32_t ab = t & 1, aph = (t >> 1) & 1;
+                if (p.early_trigger && item + gridDim.x >= n_items) pdl_launch_dependents();
                 __syncwarp();  // the previous item's reads of bw are done
 #pragma unroll
                 for (uint32_t c = 0; c < N_TILE / 32; ++c) {
@@ -493,6 +498,7 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
         for (uint32_t item = blockIdx.x; item < n_items; item += gridDim.x, ++t) {
             const Item it = decode_item(p, item, N_TILE);
             const uint32_t ab = t & 1, aph = (t >> 1) & 1;
+            if (p.early_trigger && item + gridDim.x >= n_items) pdl_launch_dependents();
             // The bias values are fetched one chunk ahead, the first before the accumulator is
             // waited for: a miss to DRAM would otherwise sit on the critical path of every chunk.
             auto load_bias = [&](uint32_t c) -> float4 {
@@ -906,6 +912,13 @@ cudaError_t launch_umma(const LutArgs& a, const CUtensorMap& lut_t_map, const Um
     const uint64_t items = (uint64_t)p.tiles_m * p.tiles_n * split;
     const uint32_t cap = plan.max_ctas ? plan.max_ctas : 148u;
     const uint32_t grid = (uint32_t)(items < cap ? items : cap);
+    // With one tile per CTA every role reaches the end of its main loop at about the same time on every SM;
+    // from there on only the epilogue runs, and the next kernel of the stream - the next operator's search, a
+    // programmatic dependent - may as well be launched: its CTAs stage their centroids on whatever SMs are or
+    // become free and then wait for this grid to complete (BERT-base step -2 % with a warm L2, -4 % with the
+    // L2 evicted).  With several tiles per CTA the CTAs finish an item apart, the early CTAs of the next kernel
+    // pile up on the SMs that are free first, and its load is skewed for good (BERT-large step +4 %): not there.
+    p.early_trigger = (items <= cap) ? 1u : 0u;
     if (sps == 2 && items > grid && ((p.slabs_per_item & 1u) || (p.slabs_total & 1u))) sps = 1;
     while (p.groups > 1 && p.a_slots % (p.groups * sps) != 0) --p.groups;
     if (split > 1 && (!acc_scratch || !tile_counters)) { *why = "tcgen05 variant: split > 1 needs scratch"; return cudaErrorInvalidValue; }
