@@ -153,28 +153,27 @@ lut_onehot_umma_kernel(const __grid_constant__ CUtensorMap lut_t_map, const Umma
     const uint32_t kAgenGroups = p.groups;
     const uint32_t kFirstEpiWarp = kFirstAgenWarp + 4 * kAgenGroups;
 
+    // Set-up, spread over the CTA so that nothing waits for one thread: a barrier per thread of warps 2 and 3
+    // (one thread initialising all 52 took 1 400 cycles), the one-hot table by warps 4 to 8, and warp 1
+    // allocates tensor memory meanwhile; with one tile per CTA this prologue is on the critical path, since the
+    // CTA only becomes resident when the search kernel before it leaves the SM.
     if (threadIdx.x == 0) {
-        s_misc[0] = 0; s_misc[1] = 0; s_misc[2] = 0;
-        for (uint32_t k = 0; k < SA; ++k) {
-            mbar_init(a_full0 + 8 * k, 4);   // the four builder warps of the group that owns the slab
-            mbar_init(a_empty0 + 8 * k, 1);  // tcgen05.commit
-        }
-        for (uint32_t j = 0; j < SB; ++j) {
-            mbar_init(b_full0 + 8 * j, 1);   // the producer's arrive.expect_tx; the TMA completes the bytes
-            mbar_init(b_empty0 + 8 * j, 1);  // tcgen05.commit
-        }
-        for (uint32_t b = 0; b < 2; ++b) {
-            mbar_init(acc_full0 + 8 * b, kMmaWarps);   // one tcgen05.commit per issuing warp
-            mbar_init(acc_empty0 + 8 * b, kEpiWarps);
-        }
-        fence_barrier_init();
+        s_misc[1] = 0; s_misc[2] = 0;   // [0] is written by tcgen05.alloc
         tma_prefetch_desc(&lut_t_map);
     }
-    if (threadIdx.x >= 32 && threadIdx.x < 32 + kOneHotRows * 8) {
-        const uint32_t e = (threadIdx.x - 32) >> 3, copy = (threadIdx.x - 32) & 7u;
+    if (threadIdx.x >= 64 && threadIdx.x < 64 + kNumBarriers) {
+        const uint32_t b = threadIdx.x - 64;
+        // a_full: the four builder warps of the group that owns the slab; a_empty, b_empty: one tcgen05.commit;
+        // b_full: the producer's arrive.expect_tx (the TMA completes the bytes); acc_full: one commit per
+        // issuing warp; acc_empty: the epilogue warps
+        const uint32_t count = b < kMaxASlots ? 4u : b < 2 * kMaxASlots + 2 * kMaxBSlots ? 1u : b < 2 * kMaxASlots + 2 * kMaxBSlots + 2 ? kMmaWarps : kEpiWarps;
+        mbar_init(a_full0 + 8 * b, count);
+        fence_barrier_init();
+    }
+    if (threadIdx.x >= 128 && threadIdx.x < 128 + kOneHotRows * 8) {
+        const uint32_t e = (threadIdx.x - 128) >> 3, copy = (threadIdx.x - 128) & 7u;
         *reinterpret_cast<uint4*>(s_tab + e * 128 + copy * 16) = onehot16(e);
     }
-    __syncthreads();
     if (warp == 1) {
         tmem_alloc(smem_u32(s_misc), kTmemCols);
         tmem_relinquish();
