@@ -62,7 +62,15 @@ constexpr int kRegThreads = 128;
 // kTok tokens are in flight per thread, which gives the scheduler kTok independent dependency
 // chains per warp.
 
-template <int V, int CT, bool TILED, int kTok>
+// Whether an instance keeps its (negated) centroids in shared memory rather than in registers: see the kernel.
+__host__ __device__ constexpr bool cent_in_smem(int V, int CT) { return (V % 2 == 0) && (CT * V >= 64 || (V >= 4 && CT * V >= 32)); }
+
+// TOKW: the CTA takes 32 codebooks and its four warps take different tokens, so that the four share one copy of the
+// centroids in shared memory (8.7 KB per CTA instead of 34.8 KB: shared memory no longer limits how many CTAs an SM
+// holds, and the staging reads a quarter of the bytes).  Otherwise the CTA takes 128 codebooks, one per thread.
+// Measured: up to 8192 tokens TOKW is 3-22 % faster (BERT-large linears 29.0 -> 27.0 us, 78.2 -> 76.2 us; 1024 tokens
+// 13.7 -> 10.7 us), at 65536 tokens 3-5 % slower; the launcher chooses by token count.
+template <int V, int CT, bool TILED, int kTok, bool TOKW = false>
 __global__ void __launch_bounds__(kRegThreads)
 ccs_reg_kernel(const float* __restrict__ x, const float* __restrict__ cent, void* __restrict__ out, uint32_t M,
                uint32_t K, uint32_t CB, uint32_t tokens_per_cta, uint32_t n_stile, uint32_t cb_mtile) {
@@ -75,10 +83,14 @@ ccs_reg_kernel(const float* __restrict__ x, const float* __restrict__ cent, void
     // overlap that kernel's tail.  Everything else it reads or overwrites - the activations, the index buffer
     // the previous LUT kernel may still be reading - comes after griddepcontrol.wait below, which returns
     // once the preceding grid has completed and its writes are visible.
-    const uint32_t cb = blockIdx.x * kRegThreads + threadIdx.x;
-    const bool active = cb < CB;
-    const uint32_t m0 = blockIdx.y * tokens_per_cta;
+    // tokens_per_cta is the run of ONE thread: the CTA's run, or each warp's where the warps take different tokens
+    static_assert(!TOKW || cent_in_smem(V, CT), "warps on different tokens share centroids through shared memory");
+    constexpr uint32_t kCbCta = TOKW ? 32u : (uint32_t)kRegThreads, kTokWarps = TOKW ? (uint32_t)kRegThreads / 32u : 1u;
+    const uint32_t col = kTokWarps > 1 ? (threadIdx.x & 31u) : threadIdx.x;   // codebook of the CTA this thread works on
+    const uint32_t cb = blockIdx.x * kCbCta + col;
+    const uint32_t m0 = (blockIdx.y * kTokWarps + (kTokWarps > 1 ? threadIdx.x >> 5 : 0u)) * tokens_per_cta;
     const uint32_t m1 = min(M, m0 + tokens_per_cta);
+    const bool active = cb < CB && m0 < M;
 
     float xs[kTok][V];
     const float* xp = x + (size_t)(active ? cb : 0) * V;
@@ -99,12 +111,12 @@ ccs_reg_kernel(const float* __restrict__ x, const float* __restrict__ cent, void
     // (kRow + 4 words for 16-byte loads: the eight threads of a quarter warp land in eight different
     // four-bank groups; kRow + 2 for 8-byte loads: the sixteen threads of a half warp in sixteen pairs).
     constexpr int kVec = (V % 4 == 0) ? 4 : 2;   // floats per shared-memory load of a centroid
-    constexpr bool kCentInSmem = (V % 2 == 0) && (kRow >= 64 || (V >= 4 && kRow >= 32));
+    constexpr bool kCentInSmem = cent_in_smem(V, CT);
     constexpr int kPitch = kCentInSmem ? kRow + kVec : kRow + 1;
-    __shared__ __align__(16) float s_cent[kRegThreads * kPitch];
+    __shared__ __align__(16) float s_cent[kCbCta * kPitch];
     {
-        const uint32_t cb0 = blockIdx.x * kRegThreads;
-        const uint32_t n_cb = min((uint32_t)kRegThreads, CB - cb0);
+        const uint32_t cb0 = blockIdx.x * kCbCta;
+        const uint32_t n_cb = min(kCbCta, CB - cb0);
         const float* gp = cent + (size_t)cb0 * kRow;
         for (uint32_t e = threadIdx.x; e < n_cb * kRow; e += kRegThreads) {
             const uint32_t r = e / kRow, i = e % kRow;
@@ -118,7 +130,7 @@ ccs_reg_kernel(const float* __restrict__ x, const float* __restrict__ cent, void
     __syncthreads();
     if (!active) return;
     float nc[kCentInSmem ? 1 : CT][V];
-    const float* my_cent = s_cent + threadIdx.x * kPitch;
+    const float* my_cent = s_cent + col * kPitch;
     if constexpr (!kCentInSmem) {
 #pragma unroll
         for (int ct = 0; ct < CT; ++ct)
@@ -296,8 +308,9 @@ cudaError_t launch_dependent(void (*k)(KArgs...), dim3 grid, dim3 block, size_t 
     return cudaLaunchKernelEx(&cfg, k, static_cast<KArgs>(args)...);
 }
 
-template <int V, int CT, int kTok>
+template <int V, int CT, int kTok, bool TOKW>
 cudaError_t run_reg_tok(const CcsArgs& a, cudaStream_t s) {
+    constexpr uint32_t kCbCta = TOKW ? 32u : (uint32_t)kRegThreads, kTokWarps = TOKW ? (uint32_t)kRegThreads / 32u : 1u;
     // Run length per thread.  The grid is sized in whole waves of what the GPU holds at once - SMs x CTAs
     // resident per SM for this instance (registers and shared memory decide: 6 to 8) - because a last wave
     // that is a third full costs as much as a full one: a small batch is spread over as many CTAs as it has
@@ -310,25 +323,25 @@ cudaError_t run_reg_tok(const CcsArgs& a, cudaStream_t s) {
             int dev = 0, r = 0;
             cudaGetDevice(&dev);
             cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&r, ccs_reg_kernel<V, CT, false, kTok>, kRegThreads, 0) != cudaSuccess || r < 1) r = 4;
+            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&r, ccs_reg_kernel<V, CT, false, kTok, TOKW>, kRegThreads, 0) != cudaSuccess || r < 1) r = 4;
             if (sms < 1) sms = 148;
             resident = r;
         }
-        const uint64_t cb_blocks = (a.CB + kRegThreads - 1) / kRegThreads;
+        const uint64_t cb_blocks = (a.CB + kCbCta - 1) / kCbCta;
         const uint64_t wave = (uint64_t)sms * resident;
-        constexpr uint64_t kCap = 128;
-        const uint64_t ctas_at_cap = cb_blocks * ((a.M + kCap - 1) / kCap);
+        constexpr uint64_t kCap = 128;   // longest run of one thread
+        const uint64_t ctas_at_cap = cb_blocks * ((a.M + kCap * kTokWarps - 1) / (kCap * kTokWarps));
         const uint64_t waves = ctas_at_cap <= wave ? 1 : (ctas_at_cap + wave - 1) / wave;
-        tpt = (uint32_t)(((uint64_t)a.M * cb_blocks + waves * wave - 1) / (waves * wave));
+        tpt = (uint32_t)(((uint64_t)a.M * cb_blocks + waves * wave * kTokWarps - 1) / (waves * wave * kTokWarps));
         if (tpt < (uint32_t)kTok) tpt = kTok;
         if (tpt > kCap) tpt = kCap;
     }
     tpt = (tpt + kTok - 1) / kTok * kTok;
-    dim3 grid((a.CB + kRegThreads - 1) / kRegThreads, (a.M + tpt - 1) / tpt);
+    dim3 grid((a.CB + kCbCta - 1) / kCbCta, (a.M + tpt * kTokWarps - 1) / (tpt * kTokWarps));
     if (a.format == LUTAMM_INDEX_U16_TILED)
-        return launch_dependent(ccs_reg_kernel<V, CT, true, kTok>, grid, dim3(kRegThreads), 0, s, a.x, a.centroid, a.idx_out,
+        return launch_dependent(ccs_reg_kernel<V, CT, true, kTok, TOKW>, grid, dim3(kRegThreads), 0, s, a.x, a.centroid, a.idx_out,
                                 a.M, a.K, a.CB, tpt, a.n_stile, a.cb_mtile);
-    return launch_dependent(ccs_reg_kernel<V, CT, false, kTok>, grid, dim3(kRegThreads), 0, s, a.x, a.centroid, a.idx_out,
+    return launch_dependent(ccs_reg_kernel<V, CT, false, kTok, TOKW>, grid, dim3(kRegThreads), 0, s, a.x, a.centroid, a.idx_out,
                             a.M, a.K, a.CB, tpt, a.n_stile, a.cb_mtile);
 }
 
@@ -336,7 +349,10 @@ template <int V, int CT>
 cudaError_t run_reg(const CcsArgs& a, cudaStream_t s) {
     // Four tokens in flight per thread: their activations are loaded together (one round trip to
     // memory instead of four) and their scans interleave.  Two or one measured no faster.
-    return run_reg_tok<V, CT, 4>(a, s);
+    if constexpr (cent_in_smem(V, CT)) {
+        if (a.M <= 16384) return run_reg_tok<V, CT, 4, true>(a, s);
+    }
+    return run_reg_tok<V, CT, 4, false>(a, s);
 }
 
 template <int V>
