@@ -68,8 +68,9 @@ __host__ __device__ constexpr bool cent_in_smem(int V, int CT) { return (V % 2 =
 // TOKW: the CTA takes 32 codebooks and its four warps take different tokens, so that the four share one copy of the
 // centroids in shared memory (8.7 KB per CTA instead of 34.8 KB: shared memory no longer limits how many CTAs an SM
 // holds, and the staging reads a quarter of the bytes).  Otherwise the CTA takes 128 codebooks, one per thread.
-// Measured: up to 8192 tokens TOKW is 3-22 % faster (BERT-large linears 29.0 -> 27.0 us, 78.2 -> 76.2 us; 1024 tokens
-// 13.7 -> 10.7 us), at 65536 tokens 3-5 % slower; the launcher chooses by token count.
+// Measured with the centroids in shared memory: up to 8192 tokens TOKW is 3-22 % faster (BERT-large linears 29.0 ->
+// 27.0 us, 78.2 -> 76.2 us; 1024 tokens 13.7 -> 10.7 us), at 65536 tokens 3-5 % slower; the launcher chooses by
+// token count.
 template <int V, int CT, bool TILED, int kTok, bool TOKW = false>
 __global__ void __launch_bounds__(kRegThreads)
 ccs_reg_kernel(const float* __restrict__ x, const float* __restrict__ cent, void* __restrict__ out, uint32_t M,
@@ -84,7 +85,6 @@ ccs_reg_kernel(const float* __restrict__ x, const float* __restrict__ cent, void
     // the previous LUT kernel may still be reading - comes after griddepcontrol.wait below, which returns
     // once the preceding grid has completed and its writes are visible.
     // tokens_per_cta is the run of ONE thread: the CTA's run, or each warp's where the warps take different tokens
-    static_assert(!TOKW || cent_in_smem(V, CT), "warps on different tokens share centroids through shared memory");
     constexpr uint32_t kCbCta = TOKW ? 32u : (uint32_t)kRegThreads, kTokWarps = TOKW ? (uint32_t)kRegThreads / 32u : 1u;
     const uint32_t col = kTokWarps > 1 ? (threadIdx.x & 31u) : threadIdx.x;   // codebook of the CTA this thread works on
     const uint32_t cb = blockIdx.x * kCbCta + col;
@@ -349,9 +349,9 @@ template <int V, int CT>
 cudaError_t run_reg(const CcsArgs& a, cudaStream_t s) {
     // Four tokens in flight per thread: their activations are loaded together (one round trip to
     // memory instead of four) and their scans interleave.  Two or one measured no faster.
-    if constexpr (cent_in_smem(V, CT)) {
-        if (a.M <= 16384) return run_reg_tok<V, CT, 4, true>(a, s);
-    }
+    // The instances with their centroids in registers gain from the shared copy only while the staging is a
+    // large part of the kernel: 512 tokens x 768 features 10.7 -> 8.6 us, 12608 tokens 33.2 -> 35.2 us.
+    if (a.M <= (cent_in_smem(V, CT) ? 16384u : 512u)) return run_reg_tok<V, CT, 4, true>(a, s);
     return run_reg_tok<V, CT, 4, false>(a, s);
 }
 
